@@ -1,0 +1,318 @@
+// Bidirectional softmax attention over image + caption tokens, flash style on tcgen05
+// (replaces NextDit::attention_seq, crates/cortiq-engine/src/dit.rs:846-922, and the facade's
+// dit_attention, crates/cortiq-engine/src/gpu.rs:2332).  The n x n score matrix is never
+// materialized; segments (independent sequences in one tall batch) never see each other.
+//
+// One CTA owns 256 queries of one (segment, head): two 128-row query tiles A and B that share
+// every K / V^T tile brought in by TMA.  Per key tile of 128:
+//   S = Q K^T      tcgen05.mma, Q and K from shared memory (64-byte swizzle atoms of 32 dims,
+//                  so head_dim 96 needs no padding), 128 x 128 f32 into TMEM
+//   softmax        four warps per query tile, one query row per thread: tcgen05.ld the row,
+//                  running max / sum in the exp2 domain, P packed to bf16 and written back
+//                  over the S columns with tcgen05.st
+//   R = P V        tcgen05.mma with P as the TMEM A operand and V^T (keys contiguous, 128-byte
+//                  swizzle) from shared memory, into a per-tile TMEM scratch
+//   O = O*alpha+R  in registers (f32), so rescaling never touches TMEM
+// While the softmax warps of tile A work, the tensor core runs tile B, and vice versa.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace cmfc {
+namespace {
+
+constexpr int QT = 128;   // query rows per tile (UMMA M)
+constexpr int KT = 128;   // keys per tile (UMMA N for S, K extent for P V)
+constexpr int KV_STAGES = 2;
+constexpr int ATTN_THREADS = 32 * 10;  // TMA, MMA, 4 softmax warps for tile A, 4 for tile B
+// TMEM columns: S (and P over it) of tile A / B at 0 / 128, the P V scratch at 256 / 384
+__host__ __device__ constexpr int s_col(int t) { return t * 128; }
+__host__ __device__ constexpr int r_col(int t) { return 256 + t * 128; }
+constexpr int ATTN_TMEM_COLS = 512;
+
+struct AttnBars {
+    uint64_t q_full;
+    uint64_t k_full[KV_STAGES], k_empty[KV_STAGES];
+    uint64_t v_full[KV_STAGES], v_empty[KV_STAGES];
+    uint64_t s_full[2], p_full[2], r_full[2], r_empty[2];
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+};
+
+template <int HD>
+struct AttnSmem {
+    static constexpr int ATOMS = HD / 32;
+    static constexpr int Q_TILE = ATOMS * QT * 64;     // bytes of one query tile
+    static constexpr int K_TILE = ATOMS * KT * 64;
+    static constexpr int V_TILE = 2 * HD * 128;        // two boxes of HD rows x 64 keys
+    static constexpr int TOTAL = 2 * Q_TILE + KV_STAGES * (K_TILE + V_TILE) + 1024 + 256;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(ATTN_THREADS, 1)
+attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                 const __grid_constant__ CUtensorMap tm_vt, AttnParams p) {
+    using L = AttnSmem<HD>;
+    const int seg = blockIdx.z, head = blockIdx.y;
+    const int seg0 = p.seg_start[seg];
+    const int seg_len = p.seg_start[seg + 1] - seg0;
+    const int q0 = blockIdx.x * 2 * QT;
+    if (q0 >= seg_len) return;  // uniform for the CTA, before any barrier or TMEM use
+    const int vt0 = p.seg_start[p.nseg + 1 + seg];  // first V^T column of this segment (8-aligned)
+    const int kvh = head / (p.nh / p.nkv);
+    const int nk = (seg_len + KT - 1) / KT;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* q_smem = smem;
+    uint8_t* k_smem = q_smem + 2 * L::Q_TILE;
+    uint8_t* v_smem = k_smem + KV_STAGES * L::K_TILE;
+    AttnBars* bars = reinterpret_cast<AttnBars*>(v_smem + KV_STAGES * L::V_TILE);
+    volatile uint32_t* abort_flag = &bars->abort_flag;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&bars->q_full, 1);
+        for (int s = 0; s < KV_STAGES; ++s) {
+            mbar_init(&bars->k_full[s], 1);
+            mbar_init(&bars->k_empty[s], 1);
+            mbar_init(&bars->v_full[s], 1);
+            mbar_init(&bars->v_empty[s], 1);
+        }
+        for (int t = 0; t < 2; ++t) {
+            mbar_init(&bars->s_full[t], 1);
+            mbar_init(&bars->p_full[t], 4);
+            mbar_init(&bars->r_full[t], 1);
+            mbar_init(&bars->r_empty[t], 4);
+        }
+        bars->abort_flag = 0;
+        mbar_fence_init();
+        tma_prefetch_desc(&tm_q);
+        tma_prefetch_desc(&tm_k);
+        tma_prefetch_desc(&tm_vt);
+    }
+    if (warp == 1) {
+        tmem_alloc(&bars->tmem_base, ATTN_TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = bars->tmem_base;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (elect_one()) {
+            mbar_expect_tx(&bars->q_full, 2 * L::Q_TILE);
+            for (int t = 0; t < 2; ++t)
+                for (int a = 0; a < L::ATOMS; ++a)
+                    tma_load_2d(q_smem + t * L::Q_TILE + a * QT * 64, &tm_q, &bars->q_full, head * HD + 32 * a,
+                                seg0 + q0 + t * QT);
+            for (int j = 0; j < nk; ++j) {
+                const int s = j % KV_STAGES;
+                const uint32_t ph = (j / KV_STAGES) & 1u;
+                if (!mbar_wait(&bars->k_empty[s], ph ^ 1u, abort_flag, 11)) break;
+                mbar_expect_tx(&bars->k_full[s], L::K_TILE);
+                for (int a = 0; a < L::ATOMS; ++a)
+                    tma_load_2d(k_smem + s * L::K_TILE + a * KT * 64, &tm_k, &bars->k_full[s], kvh * HD + 32 * a,
+                                seg0 + j * KT);
+                if (!mbar_wait(&bars->v_empty[s], ph ^ 1u, abort_flag, 12)) break;
+                mbar_expect_tx(&bars->v_full[s], L::V_TILE);
+                for (int b = 0; b < 2; ++b)
+                    tma_load_2d(v_smem + s * L::V_TILE + b * HD * 128, &tm_vt, &bars->v_full[s], vt0 + j * KT + 64 * b,
+                                kvh * HD);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (elect_one()) {
+            constexpr uint32_t IDESC_S = idesc_bf16_f32(QT, KT);
+            constexpr uint32_t IDESC_R = idesc_bf16_f32(QT, HD);
+            auto issue_s = [&](int t, int s) {
+                const uint32_t qa = smem_u32(q_smem + t * L::Q_TILE), ka = smem_u32(k_smem + s * L::K_TILE);
+#pragma unroll
+                for (int a = 0; a < L::ATOMS; ++a)
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+                        mma_ss(tmem + s_col(t), smem_desc_kmajor(qa + a * QT * 64 + h * 32, 64),
+                               smem_desc_kmajor(ka + a * KT * 64 + h * 32, 64), IDESC_S, (a | h) != 0);
+            };
+            auto issue_r = [&](int t, int s) {
+                const uint32_t va = smem_u32(v_smem + s * L::V_TILE);
+#pragma unroll
+                for (int kk = 0; kk < KT / 16; ++kk)
+                    mma_ts(tmem + r_col(t), tmem + s_col(t) + kk * 8,
+                           smem_desc_kmajor(va + (kk >> 2) * HD * 128 + (kk & 3) * 32, 128), IDESC_R, kk != 0);
+            };
+            bool ok = mbar_wait(&bars->q_full, 0, abort_flag, 13);
+            if (ok) ok = mbar_wait(&bars->k_full[0], 0, abort_flag, 14);
+            if (ok) {
+                tc_fence_after();
+                issue_s(0, 0);
+                tc_commit(&bars->s_full[0]);
+                issue_s(1, 0);
+                tc_commit(&bars->s_full[1]);
+                tc_commit(&bars->k_empty[0]);
+            }
+            for (int j = 0; ok && j < nk; ++j) {
+                const int s = j % KV_STAGES;
+                const uint32_t ph = (j / KV_STAGES) & 1u, jp = j & 1u;
+                const bool more = j + 1 < nk;
+                const int s1 = (j + 1) % KV_STAGES;
+                const uint32_t ph1 = ((j + 1) / KV_STAGES) & 1u;
+                if (!mbar_wait(&bars->v_full[s], ph, abort_flag, 15)) { ok = false; break; }
+                if (more && !mbar_wait(&bars->k_full[s1], ph1, abort_flag, 16)) { ok = false; break; }
+                for (int t = 0; t < 2; ++t) {
+                    // P_t(j) is in TMEM and R_t's scratch has been drained of tile j-1
+                    if (!mbar_wait(&bars->p_full[t], jp, abort_flag, 17)) { ok = false; break; }
+                    if (j > 0 && !mbar_wait(&bars->r_empty[t], (j - 1) & 1u, abort_flag, 18)) { ok = false; break; }
+                    tc_fence_after();
+                    issue_r(t, s);
+                    tc_commit(&bars->r_full[t]);
+                    if (more) {
+                        issue_s(t, s1);
+                        tc_commit(&bars->s_full[t]);
+                    }
+                }
+                if (!ok) break;
+                tc_commit(&bars->v_empty[s]);
+                if (more) tc_commit(&bars->k_empty[s1]);
+            }
+        }
+    } else {
+        // ---------------- softmax + accumulate warps ----------------
+        const int t = (warp - 2) >> 2;          // query tile A / B
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;    // query row inside the tile
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        const float c = p.scale * 1.4426950408889634f;  // softmax in the exp2 domain
+        float m_run = -INFINITY, l_run = 0.0f, alpha_prev = 1.0f;
+        float o[HD];
+#pragma unroll
+        for (int d = 0; d < HD; ++d) o[d] = 0.0f;
+        bool ok = true;
+        auto drain = [&](float alpha) {
+#pragma unroll
+            for (int ch = 0; ch < HD / 32; ++ch) {
+                uint32_t v[32];
+                tmem_ld_x32(tmem + lane_addr + r_col(t) + ch * 32, v);
+                tc_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[ch * 32 + i] = o[ch * 32 + i] * alpha + __uint_as_float(v[i]);
+            }
+        };
+        for (int j = 0; j < nk; ++j) {
+            const uint32_t jp = j & 1u;
+            if (!mbar_wait(&bars->s_full[t], jp, abort_flag, 19)) { ok = false; break; }
+            tc_fence_after();
+            if (j > 0) {
+                // R(j-1) finished before S(j) (same issue queue); fold it in and free the scratch
+                if (!mbar_wait(&bars->r_full[t], (j - 1) & 1u, abort_flag, 20)) { ok = false; break; }
+                tc_fence_after();
+                drain(alpha_prev);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars->r_empty[t]);
+            }
+            const int kbase = j * KT;
+            const int valid = seg_len - kbase;  // keys of this tile inside the segment
+            // pass 1: row maximum
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int ch = 0; ch < 4; ++ch) {
+                uint32_t v[32];
+                tmem_ld_x32(tmem + lane_addr + s_col(t) + ch * 32, v);
+                tc_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    if (ch * 32 + i < valid) mx = fmaxf(mx, __uint_as_float(v[i]));
+            }
+            const float m_new = fmaxf(m_run, mx * c);
+            alpha_prev = exp2f(m_run - m_new);  // 0 on the first tile (m_run = -inf)
+            float sum = 0.0f;
+            // pass 2: probabilities, packed to bf16 over the S columns already consumed
+#pragma unroll 1
+            for (int ch = 0; ch < 4; ++ch) {
+                uint32_t v[32];
+                tmem_ld_x32(tmem + lane_addr + s_col(t) + ch * 32, v);
+                tc_wait_ld();
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float e0 = (ch * 32 + i < valid) ? exp2f(__uint_as_float(v[i]) * c - m_new) : 0.0f;
+                    float e1 = (ch * 32 + i + 1 < valid) ? exp2f(__uint_as_float(v[i + 1]) * c - m_new) : 0.0f;
+                    sum += e0 + e1;
+                    pk[i >> 1] = pack_bf16(e0, e1);
+                }
+                tmem_st_x16(tmem + lane_addr + s_col(t) + ch * 16, pk);
+            }
+            tc_wait_st();
+            l_run = l_run * alpha_prev + sum;
+            m_run = m_new;
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->p_full[t]);
+        }
+        if (ok && mbar_wait(&bars->r_full[t], (nk - 1) & 1u, abort_flag, 21)) {
+            tc_fence_after();
+            drain(alpha_prev);
+            const int qrow = q0 + t * QT + row;
+            if (qrow < seg_len) {
+                const float inv = 1.0f / l_run;
+                __nv_bfloat16* dst = p.out + ((size_t)(seg0 + qrow) * p.nh + head) * HD;
+#pragma unroll
+                for (int d = 0; d < HD; d += 8) {
+                    uint4 w;
+                    w.x = pack_bf16(o[d] * inv, o[d + 1] * inv);
+                    w.y = pack_bf16(o[d + 2] * inv, o[d + 3] * inv);
+                    w.z = pack_bf16(o[d + 4] * inv, o[d + 5] * inv);
+                    w.w = pack_bf16(o[d + 6] * inv, o[d + 7] * inv);
+                    *reinterpret_cast<uint4*>(dst + d) = w;
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem, ATTN_TMEM_COLS);
+    }
+    if (threadIdx.x == 0 && bars->abort_flag) atomicCAS(p.status, 0u, 0x200u | bars->abort_flag);
+}
+
+}  // namespace
+
+int attn_smem_bytes(int hd) {
+    switch (hd) {
+        case 32: return AttnSmem<32>::TOTAL;
+        case 64: return AttnSmem<64>::TOTAL;
+        case 96: return AttnSmem<96>::TOTAL;
+        case 128: return AttnSmem<128>::TOTAL;
+        default: return 0;
+    }
+}
+
+template <int HD>
+static int launch_hd(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_vt, const AttnParams& p,
+                     cudaStream_t stream) {
+    CMFC_CUDA(cudaFuncSetAttribute(attention_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   AttnSmem<HD>::TOTAL));
+    dim3 grid((p.max_seg + 2 * QT - 1) / (2 * QT), p.nh, p.nseg);
+    attention_kernel<HD><<<grid, ATTN_THREADS, AttnSmem<HD>::TOTAL, stream>>>(tm_q, tm_k, tm_vt, p);
+    CMFC_CUDA(cudaGetLastError());
+    return OK;
+}
+
+int launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_vt, const AttnParams& p,
+                     cudaStream_t stream) {
+    switch (p.hd) {
+        case 32: return launch_hd<32>(tm_q, tm_k, tm_vt, p, stream);
+        case 64: return launch_hd<64>(tm_q, tm_k, tm_vt, p, stream);
+        case 96: return launch_hd<96>(tm_q, tm_k, tm_vt, p, stream);
+        case 128: return launch_hd<128>(tm_q, tm_k, tm_vt, p, stream);
+        default: return fail(ERR_UNSUPPORTED, "attention: head_dim must be 32, 64, 96 or 128");
+    }
+}
+
+}  // namespace cmfc

@@ -1,0 +1,308 @@
+// Dequant-fused GEMM for the quantized linears of the NextDiT block:
+//     Y[M, N] = X[M, K] . dequant(W[N, K])^T
+// (replaces QTensor::matmat's Q8Row / Q4Tiled / Q4TiledP arms,
+//  crates/cortiq-engine/src/qtensor.rs:1441-1861).
+//
+// The product is computed transposed, D[n, m] = W[n, :] . X[m, :], so that the dequantized
+// weights are the tcgen05 A operand (one weight row per TMEM lane) and the activations are
+// the B operand:
+//   * X (bf16, K-major) tiles of 256 tokens x 64 k arrive by TMA with the 128-byte swizzle
+//     and are consumed by the tensor core straight from shared memory;
+//   * the packed weight tile of 128 rows x 64 k (int8, or 4-bit nibbles plus a per-group f32
+//     scale) arrives by TMA as raw bytes; eight dequant warps, one weight row per thread,
+//     unpack it in registers to bf16 and write it to TENSOR MEMORY with tcgen05.st;
+//   * one elected thread issues tcgen05.mma (A from TMEM, B from SMEM, 128 x 256 x 16) into a
+//     256-column f32 accumulator in TMEM;
+//   * the same eight warps drain the accumulator with tcgen05.ld and store Y (f32 or bf16, or
+//     the fused SwiGLU product when the weight rows interleave W1 and W3).
+// Persistent: grid = min(#tiles, #SMs); each CTA walks tiles blockIdx.x, +gridDim.x, ...
+//
+// bf16 operand definition: RN_bf16(exact f32 dequantized weight).  For q8 the integer level
+// itself is the operand (exact in bf16) and the f32 row scale is applied to the accumulator.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace cmfc {
+namespace {
+
+constexpr int TW = 128;     // weight rows per tile  (UMMA M, TMEM lanes)
+constexpr int TT = 256;     // tokens per tile       (UMMA N, accumulator columns)
+constexpr int BK = 64;      // k per pipeline stage  (one 128-byte swizzle atom of bf16)
+constexpr int STAGES = 4;
+constexpr int X_STAGE = TT * BK * 2;   // 32 KiB
+constexpr int W_STAGE = TW * BK;       // 8 KiB (q8: 64 B/row; q4 uses the first 4 KiB)
+constexpr int S_STAGE = 2 * TW * 4;    // 1 KiB (q4: two groups x 128 rows of f32 scales)
+constexpr int ACC_COL = 0;
+constexpr int A_COL = 256;             // four A stages of 32 columns (64 bf16) each
+constexpr int TMEM_COLS = 512;
+constexpr int NUM_DQ_WARPS = 8;
+constexpr int THREADS = 32 * (2 + NUM_DQ_WARPS);
+constexpr int SMEM_BYTES = STAGES * (X_STAGE + W_STAGE + S_STAGE) + 1024 /*align*/ + 256 /*barriers*/;
+
+struct Bars {
+    uint64_t full[STAGES];
+    uint64_t empty[STAGES];
+    uint64_t a_full[STAGES];
+    uint64_t acc_full;
+    uint64_t acc_empty;
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+};
+
+// ---- register unpack: 32 consecutive k of one weight row -> 16 packed bf16x2 ----
+
+// int8 -> bf16 without a conversion instruction: for byte b, 0x4300|(b&0x7f) is the bf16
+// 128+(b&0x7f) and 0x4300|(b&0x80) is 128 or 256; their difference is the signed level.
+__device__ __forceinline__ void unpack_q8_word(uint32_t w, uint32_t& o0, uint32_t& o1) {
+    uint32_t t0 = __byte_perm(w, 0u, 0x4140);
+    uint32_t t1 = __byte_perm(w, 0u, 0x4342);
+    uint32_t v0 = (t0 & 0x007f007fu) | 0x43004300u, c0 = (t0 & 0x00800080u) | 0x43004300u;
+    uint32_t v1 = (t1 & 0x007f007fu) | 0x43004300u, c1 = (t1 & 0x00800080u) | 0x43004300u;
+    asm("sub.bf16x2 %0, %1, %2;" : "=r"(o0) : "r"(v0), "r"(c0));
+    asm("sub.bf16x2 %0, %1, %2;" : "=r"(o1) : "r"(v1), "r"(c1));
+}
+
+// nibble at bit position p of ``w`` -> exact f32 (nib-8)*s: the nibble is OR-ed into the
+// mantissa of 2^23, the bias (2^23 + 8*2^p) is subtracted exactly, and the result is scaled
+// by s*2^-p (a power-of-two rescale, so the single rounding equals that of (nib-8)*s).
+template <int P>
+__device__ __forceinline__ float nib_times(uint32_t w, float s_shifted) {
+    float f = __uint_as_float((w & (0xFu << P)) | 0x4B000000u);
+    f = __fsub_rn(f, 8388608.0f + 8.0f * (float)(1u << P));
+    return __fmul_rn(f, s_shifted);
+}
+
+struct Q4Scales {
+    float s0, s4, s8, s12, s16;
+    __device__ __forceinline__ explicit Q4Scales(float s)
+        : s0(s), s4(s * 0.0625f), s8(s * 0.00390625f), s12(s * 0.000244140625f), s16(s * 1.52587890625e-05f) {}
+};
+
+__device__ __forceinline__ void unpack_q4_word(uint32_t w, const Q4Scales& sc, uint32_t* o) {
+    uint32_t hi = w >> 12;
+    o[0] = pack_bf16(nib_times<0>(w, sc.s0), nib_times<4>(w, sc.s4));
+    o[1] = pack_bf16(nib_times<8>(w, sc.s8), nib_times<12>(w, sc.s12));
+    o[2] = pack_bf16(nib_times<16>(w, sc.s16), nib_times<8>(hi, sc.s8));
+    o[3] = pack_bf16(nib_times<12>(hi, sc.s12), nib_times<16>(hi, sc.s16));
+}
+
+__device__ __forceinline__ uint4 lds128(const uint8_t* p) { return *reinterpret_cast<const uint4*>(p); }
+
+__device__ __forceinline__ float silu_f(float v) { return v / (1.0f + __expf(-v)); }
+
+template <int WKIND>  // 0 = q8 (int8 plane), 1 = q4 (nibble plane + transposed f32 scales)
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_dequant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
+                    const __grid_constant__ CUtensorMap tm_s, GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* x_smem = smem;
+    uint8_t* w_smem = smem + STAGES * X_STAGE;
+    uint8_t* s_smem = w_smem + STAGES * W_STAGE;
+    Bars* bars = reinterpret_cast<Bars*>(s_smem + STAGES * S_STAGE);
+    volatile uint32_t* abort_flag = &bars->abort_flag;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int kblocks = p.K / BK;
+    const int tiles_m = (p.M + TT - 1) / TT;
+    const int tiles = tiles_m * (p.N / TW);
+    constexpr uint32_t W_BYTES = (WKIND == 0) ? TW * BK : TW * BK / 2;
+    constexpr uint32_t TX_BYTES = X_STAGE + W_BYTES + (WKIND == 1 ? S_STAGE : 0);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&bars->full[s], 1);
+            mbar_init(&bars->empty[s], 1 + NUM_DQ_WARPS);
+            mbar_init(&bars->a_full[s], NUM_DQ_WARPS);
+        }
+        mbar_init(&bars->acc_full, 1);
+        mbar_init(&bars->acc_empty, NUM_DQ_WARPS);
+        bars->abort_flag = 0;
+        mbar_fence_init();
+        tma_prefetch_desc(&tm_x);
+        tma_prefetch_desc(&tm_w);
+        if (WKIND == 1) tma_prefetch_desc(&tm_s);
+    }
+    if (warp == 1) {
+        tmem_alloc(&bars->tmem_base, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = bars->tmem_base;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (elect_one()) {
+            uint32_t it = 0;
+            for (int tile = blockIdx.x; tile < tiles && !*abort_flag; tile += gridDim.x) {
+                const int n0 = (tile / tiles_m) * TW, m0 = (tile % tiles_m) * TT;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1u;
+                    if (!mbar_wait(&bars->empty[s], ph ^ 1u, abort_flag, 1)) break;
+                    mbar_expect_tx(&bars->full[s], TX_BYTES);
+                    tma_load_2d(x_smem + s * X_STAGE, &tm_x, &bars->full[s], kb * BK, m0);
+                    if (WKIND == 0) {
+                        tma_load_2d(w_smem + s * W_STAGE, &tm_w, &bars->full[s], kb * BK, n0);
+                    } else {
+                        tma_load_2d(w_smem + s * W_STAGE, &tm_w, &bars->full[s], kb * (BK / 2), n0);
+                        tma_load_2d(s_smem + s * S_STAGE, &tm_s, &bars->full[s], n0, kb * 2);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (elect_one()) {
+            constexpr uint32_t IDESC = idesc_bf16_f32(TW, TT);
+            uint32_t it = 0, tile_i = 0;
+            for (int tile = blockIdx.x; tile < tiles && !*abort_flag; tile += gridDim.x, ++tile_i) {
+                if (tile_i > 0 && !mbar_wait(&bars->acc_empty, (tile_i - 1) & 1u, abort_flag, 2)) break;
+                tc_fence_after();
+                bool ok = true;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1u;
+                    if (!mbar_wait(&bars->full[s], ph, abort_flag, 3) ||
+                        !mbar_wait(&bars->a_full[s], ph, abort_flag, 4)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t xs = smem_u32(x_smem + s * X_STAGE);
+#pragma unroll
+                    for (int j = 0; j < BK / 16; ++j) {
+                        mma_ts(tmem + ACC_COL, tmem + A_COL + s * 32 + j * 8, smem_desc_kmajor(xs + j * 32, 128),
+                               IDESC, (kb | j) != 0);
+                    }
+                    tc_commit(&bars->empty[s]);
+                }
+                if (!ok) break;
+                tc_commit(&bars->acc_full);
+            }
+        }
+    } else {
+        // ---------------- dequant + epilogue warps ----------------
+        const int dq = warp - 2;                 // 0..7
+        const int quarter = warp & 3;            // TMEM lane quarter this warp may touch
+        const int half = dq >> 2;                // which 32 k of the 64-k stage / which 128 tokens
+        const int row = quarter * 32 + lane;     // weight row inside the tile
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        uint32_t it = 0, tile_i = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < tiles && ok && !*abort_flag; tile += gridDim.x, ++tile_i) {
+            const int n0 = (tile / tiles_m) * TW, m0 = (tile % tiles_m) * TT;
+            for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                const int s = it % STAGES;
+                const uint32_t ph = (it / STAGES) & 1u;
+                if (!mbar_wait(&bars->full[s], ph, abort_flag, 5)) { ok = false; break; }
+                uint32_t a[16];
+                if (WKIND == 0) {
+                    const uint8_t* wrow = w_smem + s * W_STAGE + row * 64;
+                    const int sw = (row >> 1) & 3;  // 64-byte swizzle: chunk ^= address bits [7,9)
+                    uint4 v0 = lds128(wrow + (((2 * half) ^ sw) << 4));
+                    uint4 v1 = lds128(wrow + (((2 * half + 1) ^ sw) << 4));
+                    unpack_q8_word(v0.x, a[0], a[1]);   unpack_q8_word(v0.y, a[2], a[3]);
+                    unpack_q8_word(v0.z, a[4], a[5]);   unpack_q8_word(v0.w, a[6], a[7]);
+                    unpack_q8_word(v1.x, a[8], a[9]);   unpack_q8_word(v1.y, a[10], a[11]);
+                    unpack_q8_word(v1.z, a[12], a[13]); unpack_q8_word(v1.w, a[14], a[15]);
+                } else {
+                    const uint8_t* wrow = w_smem + s * W_STAGE + row * 32;
+                    const int sw = (row >> 2) & 1;  // 32-byte swizzle: chunk ^= address bit 7
+                    uint4 v = lds128(wrow + ((half ^ sw) << 4));
+                    const float sc = reinterpret_cast<const float*>(s_smem + s * S_STAGE)[half * TW + row];
+                    const Q4Scales q(sc);
+                    unpack_q4_word(v.x, q, a + 0);
+                    unpack_q4_word(v.y, q, a + 4);
+                    unpack_q4_word(v.z, q, a + 8);
+                    unpack_q4_word(v.w, q, a + 12);
+                }
+                // The previous occupant of A stage s was consumed before full[s] could fire
+                // again (the producer refills a stage only after the MMAs on it committed).
+                tmem_st_x16(tmem + lane_addr + A_COL + s * 32 + half * 16, a);
+                tc_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&bars->a_full[s]);
+                    mbar_arrive(&bars->empty[s]);
+                }
+            }
+            if (!ok) break;
+            // ---- epilogue: this thread owns output channel n0+row, tokens m0+128*half+[0,128) ----
+            if (!mbar_wait(&bars->acc_full, tile_i & 1u, abort_flag, 6)) { ok = false; break; }
+            tc_fence_after();
+            const int n = n0 + row;
+            float rs = 1.0f;
+            if (WKIND == 0) rs = p.row_scale[n];
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t v[32];
+                tmem_ld_x32(tmem + lane_addr + ACC_COL + half * 128 + c * 32, v);
+                tc_wait_ld();
+                const int mb = m0 + half * 128 + c * 32;
+                if (p.mode == GEMM_OUT_F32) {
+                    float* out = reinterpret_cast<float*>(p.out) + (size_t)mb * p.ldo + n;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (mb + j < p.M) out[(size_t)j * p.ldo] = __uint_as_float(v[j]) * rs;
+                } else if (p.mode == GEMM_OUT_BF16) {
+                    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)mb * p.ldo + n;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (mb + j < p.M) out[(size_t)j * p.ldo] = __float2bfloat16_rn(__uint_as_float(v[j]) * rs);
+                } else {
+                    // GEMM_OUT_SWIGLU: even rows hold W1 (gate), odd rows W3 (up) of channel n/2.
+                    // Lanes 2i and 2i+1 swap one value per token pair; the even lane finishes
+                    // token j, the odd lane token j+1.
+                    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)mb * p.ldo + (n >> 1);
+                    const bool odd = lane & 1;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) {
+                        float mine_a = __uint_as_float(v[j]) * rs, mine_b = __uint_as_float(v[j + 1]) * rs;
+                        float got = __shfl_xor_sync(0xffffffffu, odd ? mine_a : mine_b, 1);
+                        float g = odd ? got : mine_a;
+                        float u = odd ? mine_b : got;
+                        int m = mb + j + (odd ? 1 : 0);
+                        if (m < p.M) out[(size_t)(j + (odd ? 1 : 0)) * p.ldo] = __float2bfloat16_rn(silu_f(g) * u);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->acc_empty);
+        }
+    }
+
+    // ---------------- common exit ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem, TMEM_COLS);
+    }
+    if (threadIdx.x == 0 && bars->abort_flag) atomicCAS(p.status, 0u, 0x100u | bars->abort_flag);
+}
+
+}  // namespace
+
+int gemm_smem_bytes() { return SMEM_BYTES; }
+
+int launch_gemm_dequant(int wkind, const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUtensorMap& tm_s,
+                        const GemmParams& p, int num_sms, cudaStream_t stream) {
+    if (p.K % BK != 0 || p.N % TW != 0 || p.M <= 0)
+        return fail(ERR_SHAPE, "dequant GEMM needs K % 64 == 0 and N % 128 == 0");
+    static bool configured[2] = {false, false};
+    auto kern = wkind == 0 ? gemm_dequant_kernel<0> : gemm_dequant_kernel<1>;
+    if (!configured[wkind]) {
+        CMFC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        configured[wkind] = true;
+    }
+    const int tiles = ((p.M + TT - 1) / TT) * (p.N / TW);
+    const int grid = tiles < num_sms ? tiles : num_sms;
+    kern<<<grid, THREADS, SMEM_BYTES, stream>>>(tm_x, tm_w, tm_s, p);
+    CMFC_CUDA(cudaGetLastError());
+    return OK;
+}
+
+}  // namespace cmfc

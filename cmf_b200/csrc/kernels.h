@@ -1,0 +1,105 @@
+// Launchers of the device kernels (device pointers, explicit stream).  Host-callable; the C ABI
+// in api.cu composes them.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace cmfc {
+
+// ---------------- dequant GEMM (gemm_dequant.cu) ----------------
+enum GemmMode : int { GEMM_OUT_F32 = 0, GEMM_OUT_BF16 = 1, GEMM_OUT_SWIGLU = 2 };
+
+struct GemmParams {
+    int M, N, K;             // tokens, weight rows, reduction
+    void* out;               // [M, ldo] f32 or bf16; SWIGLU writes [M, N/2] bf16
+    int ldo;
+    int mode;
+    const float* row_scale;  // q8 only: [N]
+    uint32_t* status;        // device word; a kernel that ran out of wait budget records the site
+};
+
+int gemm_smem_bytes();
+int launch_gemm_dequant(int wkind, const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUtensorMap& tm_s,
+                        const GemmParams& p, int num_sms, cudaStream_t stream);
+
+// ---------------- flash attention (attention.cu) ----------------
+struct AttnParams {
+    int nh, nkv, hd;         // hd must be a multiple of 32, <= 128
+    int n_total;             // rows of q/k (all segments)
+    int vt_pitch;            // elements per row of V^T (>= n_total, multiple of 8)
+    const int* seg_start;    // [nseg+1] device, token offsets
+    int nseg;
+    int max_seg;             // longest segment (grid sizing)
+    float scale;             // 1/sqrt(hd)
+    __nv_bfloat16* out;      // [n_total, nh*hd]
+    uint32_t* status;
+};
+int attn_smem_bytes(int hd);
+int launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_vt,
+                     const AttnParams& p, cudaStream_t stream);
+
+// ---------------- codecs (codec_kernels.cu) ----------------
+// raw container payloads -> GEMM planes
+void launch_q4t_split(const uint8_t* raw, int rows, int cols, uint8_t* nib, float* scales_t, cudaStream_t s);
+void launch_q4tp_scales(const uint8_t* codes, int code_stride, const float* ladders /*[rows,32]*/, int rows,
+                        int gpr, float* scales_t, cudaStream_t s);
+void launch_f16_to_f32(const uint16_t* h, float* out, int n, cudaStream_t s);
+// planes -> exact f32 weights [rows, cols] (the bit-exactness check)
+void launch_dequant_q8(const int8_t* q, const float* row_scale, int rows, int cols, float* out, cudaStream_t s);
+void launch_dequant_q4(const uint8_t* nib, const float* scales_t, int rows, int cols, float* out, cudaStream_t s);
+// device-side encoders (bit-exact with the reference quantizer; transcendental values come
+// from host-built lookup tables indexed by f16 bit pattern)
+void launch_encode_q8_row(const float* w, int rows, int cols, uint8_t* payload, cudaStream_t s);
+void launch_encode_q4_tiled(const float* w, int rows, int cols, uint8_t* payload, cudaStream_t s);
+void launch_encode_q4tp(const float* w, int rows, int cols, uint8_t* payload, const float* log2_lut,
+                        const float* exp2_lut, cudaStream_t s);
+
+// ---------------- element-wise / row kernels (rowops.cu) ----------------
+void launch_f32_to_bf16(const float* in, __nv_bfloat16* out, size_t n, cudaStream_t s);
+void launch_bf16_to_f32(const __nv_bfloat16* in, float* out, size_t n, cudaStream_t s);
+// out_bf16[r, :] = rms(x[r, :]; w, eps) * (1 + shift)   (shift may be null)
+void launch_rms_mod(const float* x, const float* w, const float* shift, double eps, int rows, int cols,
+                    __nv_bfloat16* out_bf16, float* out_f32, cudaStream_t s);
+// x[r, :] += gate * rms(src[r, :]; w, eps)   (gate may be null -> 1)
+void launch_gated_residual(float* x, const float* src, const float* w, const float* gate, double eps, int rows,
+                           int cols, cudaStream_t s);
+// fused: x += gate*rms(src; w_res); then out = rms(x; w_next)*(1+shift)  (one pass over x)
+void launch_residual_then_norm(float* x, const float* src, const float* w_res, const float* gate,
+                               const float* w_next, const float* shift, double eps, int rows, int cols,
+                               __nv_bfloat16* out_bf16, cudaStream_t s);
+// per (token, head): qk RMS norm (eps 1e-5) + interleaved-pair RoPE in f64; writes Q,K bf16
+// token-major and V^T bf16 [nkv*hd, vt_pitch]
+void launch_qk_rope_pack(const float* qkv, int n, int nh, int nkv, int hd, const float* norm_q,
+                         const float* norm_k, const double* cos_t, const double* sin_t, __nv_bfloat16* q,
+                         __nv_bfloat16* k, __nv_bfloat16* vt, int vt_pitch, const int* seg_table, int nseg, int max_seg,
+                         cudaStream_t s);
+// y[r] = act_out( dot(W[r, :], act_in(x)) * scale[r] + b[r] ); W f32 or int8 (+row scales)
+// act_in: 0 none, 1 silu.  tanh_lo..tanh_hi: rows in [lo0,hi0) or [lo1,hi1) get tanh.
+struct GemvParams {
+    const void* w; int w_is_q8; const float* row_scale; const float* bias; const float* x;
+    float* y; int rows, cols; int act_in; int tanh_lo0, tanh_hi0, tanh_lo1, tanh_hi1;
+};
+void launch_gemv(const GemvParams& p, cudaStream_t s);
+// small exact-f32 GEMM: Y[M,N] = A[M,K] . W[N,K]^T + b
+void launch_sgemm_nt_bias(const float* a, const float* w, const float* bias, float* y, int M, int N, int K,
+                          cudaStream_t s);
+void launch_time_freqs(float t, float* out256, cudaStream_t s);
+void launch_patchify(const float* latent, int c, int h, int w, int p, float* tok, cudaStream_t s);
+void launch_unpatchify(const float* tok, int c, int h, int w, int p, float* latent, cudaStream_t s);
+// LayerNorm without affine (eps 1e-6), times (1 + scale), f32 out
+void launch_layernorm_scale(const float* x, const float* scale, int rows, int cols, float* out, cudaStream_t s);
+void launch_silu_mul(const __nv_bfloat16* gu, int rows, int inter, __nv_bfloat16* out, cudaStream_t s);
+// CFG combine with per-row norm rescale, then Euler update: x -= d * pred
+void launch_cfg_euler(float* latents, const float* cond, const float* uncond, float gs, float d, int rows, int lw,
+                      int use_cfg, cudaStream_t s);
+void launch_transpose_head_major(const float* src_head_major, int heads, int n, int hd, float scale,
+                                 __nv_bfloat16* dst_token_major, cudaStream_t s);
+void launch_v_head_major_to_vt(const float* v_head_major, int nkv, int n, int hd, __nv_bfloat16* vt, int vt_pitch,
+                               cudaStream_t s);
+void launch_add_bias_rows(float* y, const float* bias, size_t rows, int cols, cudaStream_t s);
+void launch_fill_normal(float* out, size_t n, uint64_t seed, float std, cudaStream_t s);
+void launch_interleave_f32(float* dst, int dst_stride, int dst_off, const float* src, size_t count, cudaStream_t s);
+
+}  // namespace cmfc

@@ -1,0 +1,654 @@
+// Host runtime: errors, device contexts, the memory-mapped container reader, weight upload
+// into kernel planes, and the device-level block composed from the kernels.
+#include "runtime.h"
+
+#include <fcntl.h>
+#include <math.h>
+#include <string.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <atomic>
+
+namespace cmfc {
+
+// ---------------- errors ----------------
+static thread_local std::string g_last_error;
+void set_error(const std::string& msg) { g_last_error = msg; }
+const std::string& last_error() { return g_last_error; }
+int fail(int code, const std::string& msg) {
+    g_last_error = msg;
+    return code;
+}
+
+// ---------------- tensor maps ----------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+int make_tensor_map_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t rows, uint64_t cols,
+                       uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols, int swizzle) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return fail(ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    CUtensorMapDataType dt = elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                             : elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                               : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {pitch_bytes};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUtensorMapSwizzle sw = swizzle == 3 ? CU_TENSOR_MAP_SWIZZLE_128B
+                            : swizzle == 2 ? CU_TENSOR_MAP_SWIZZLE_64B
+                            : swizzle == 1 ? CU_TENSOR_MAP_SWIZZLE_32B
+                                           : CU_TENSOR_MAP_SWIZZLE_NONE;
+    if ((reinterpret_cast<uintptr_t>(base) & 15) || (pitch_bytes & 15))
+        return fail(ERR_BAD_ARG, "tensor map base and pitch must be 16-byte aligned");
+    CUresult r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+    return OK;
+}
+
+// ---------------- buffers ----------------
+int DevBuf::ensure(size_t bytes) {
+    if (bytes <= cap && p) return OK;
+    if (p) cudaFree(p);
+    p = nullptr;
+    cap = 0;
+    size_t want = (bytes + 255) & ~size_t(255);
+    cudaError_t e = cudaMalloc(&p, want);
+    if (e != cudaSuccess) {
+        p = nullptr;
+        return fail(ERR_OOM, std::string("cudaMalloc of ") + std::to_string(want) + " bytes: " + cudaGetErrorString(e));
+    }
+    cap = want;
+    return OK;
+}
+void DevBuf::release() {
+    if (p) cudaFree(p);
+    p = nullptr;
+    cap = 0;
+}
+
+// ---------------- contexts ----------------
+static std::mutex g_ctx_mu;
+static std::map<int, std::unique_ptr<Context>> g_ctxs;
+static thread_local int g_cur_device = -1;
+
+int ctx_set_device(int device) {
+    int count = 0;
+    CMFC_CUDA(cudaGetDeviceCount(&count));
+    if (device < 0 || device >= count) return fail(ERR_BAD_ARG, "no such CUDA device " + std::to_string(device));
+    CMFC_CUDA(cudaSetDevice(device));
+    std::lock_guard<std::mutex> lk(g_ctx_mu);
+    if (!g_ctxs.count(device)) {
+        cudaDeviceProp prop;
+        CMFC_CUDA(cudaGetDeviceProperties(&prop, device));
+        if (prop.major != 10)
+            return fail(ERR_UNSUPPORTED, std::string("this library is built for sm_100a only; device is ") + prop.name +
+                                             " (sm_" + std::to_string(prop.major) + std::to_string(prop.minor) + ")");
+        std::unique_ptr<Context> c(new Context());
+        c->device = device;
+        c->num_sms = prop.multiProcessorCount;
+        CMFC_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+        CMFC_CUDA(cudaMalloc(&c->status, 4));
+        CMFC_CUDA(cudaMemset(c->status, 0, 4));
+        CMFC_CUDA(cudaMallocHost(&c->status_host, 4));
+        // log2f / exp2f of every half-precision value, from the host's libm: the device
+        // quantizer must land on the bits the CPU encoder computes.
+        std::vector<float> l2(65536), e2(65536);
+        for (uint32_t h = 0; h < 65536; ++h) {
+            uint32_t s = (h >> 15) << 31, e = (h >> 10) & 0x1F, m = h & 0x3FF, bits;
+            if (e == 0) {
+                if (!m) bits = s;
+                else {
+                    uint32_t sh = 0;
+                    while (!(m & 0x400)) { m <<= 1; ++sh; }
+                    bits = s | ((113 - sh) << 23) | ((m & 0x3FF) << 13);
+                }
+            } else if (e == 0x1F) bits = s | 0x7F800000u | (m << 13);
+            else bits = s | ((e + 112) << 23) | (m << 13);
+            float f;
+            memcpy(&f, &bits, 4);
+            l2[h] = log2f(f);
+            e2[h] = exp2f(f);
+        }
+        CMFC_CUDA(cudaMalloc(&c->log2_lut, 65536 * 4));
+        CMFC_CUDA(cudaMalloc(&c->exp2_lut, 65536 * 4));
+        CMFC_CUDA(cudaMemcpy(c->log2_lut, l2.data(), 65536 * 4, cudaMemcpyHostToDevice));
+        CMFC_CUDA(cudaMemcpy(c->exp2_lut, e2.data(), 65536 * 4, cudaMemcpyHostToDevice));
+        g_ctxs[device] = std::move(c);
+    }
+    g_cur_device = device;
+    return OK;
+}
+
+Context* ctx() {
+    if (g_cur_device < 0) {
+        if (ctx_set_device(0) != OK) return nullptr;
+    } else {
+        cudaSetDevice(g_cur_device);
+    }
+    std::lock_guard<std::mutex> lk(g_ctx_mu);
+    auto it = g_ctxs.find(g_cur_device);
+    return it == g_ctxs.end() ? nullptr : it->second.get();
+}
+
+int check_status(Context* c, const char* what) {
+    CMFC_CUDA(cudaMemcpyAsync(c->status_host, c->status, 4, cudaMemcpyDeviceToHost, c->stream));
+    CMFC_CUDA(cudaStreamSynchronize(c->stream));
+    if (*c->status_host) {
+        uint32_t v = *c->status_host;
+        cudaMemsetAsync(c->status, 0, 4, c->stream);
+        return fail(ERR_DEVICE_WAIT, std::string(what) + ": a kernel gave up a bounded wait (site " + std::to_string(v) + ")");
+    }
+    return OK;
+}
+
+SpanGuard::SpanGuard(Context* c_, const char* name) : c(c_) {
+    if (!c->prof.on) return;
+    cudaEvent_t a, b;
+    cudaEventCreate(&a);
+    cudaEventCreate(&b);
+    cudaEventRecord(a, c->stream);
+    idx = c->prof.spans.size();
+    c->prof.spans.push_back({name, {a, b}});
+}
+SpanGuard::~SpanGuard() {
+    if (idx != (size_t)-1) cudaEventRecord(c->prof.spans[idx].second.second, c->stream);
+}
+
+// ---------------- container ----------------
+// 64-bit content hash of the container format (crates/cortiq-core/src/hash.rs:8-36): every
+// little-endian u64 word goes through the murmur3 finalizer, is XOR-ed with its index times the
+// golden-ratio constant, all are XOR-reduced, the byte length is mixed in and finalized again.
+static inline uint64_t fmix64(uint64_t x) {
+    x ^= x >> 33;
+    x *= 0xFF51AFD7ED558CCDull;
+    x ^= x >> 33;
+    x *= 0xC4CEB9FE1A85EC53ull;
+    x ^= x >> 33;
+    return x;
+}
+uint64_t hash64(const uint8_t* p, size_t n) {
+    uint64_t h = 0;
+    size_t words = (n + 7) / 8;
+    for (size_t i = 0; i < words; ++i) {
+        uint64_t w = 0;
+        size_t take = (i * 8 + 8 <= n) ? 8 : n - i * 8;
+        memcpy(&w, p + i * 8, take);
+        h ^= fmix64(w) ^ (i * 0x9E3779B97F4A7C15ull);
+    }
+    h ^= (uint64_t)n;
+    return fmix64(h);
+}
+
+size_t payload_nbytes(int dtype, size_t rows, size_t cols) {
+    switch (dtype) {
+        case DT_F32: return rows * cols * 4;
+        case DT_F16: return rows * cols * 2;
+        case DT_U8: return rows * cols;
+        case DT_Q8: return rows * cols + rows * 2;
+        case DT_Q4T: return ((rows * cols + 31) / 32) * 18;
+        case DT_Q4TP: {
+            size_t gpr = cols / 32;
+            return rows * gpr * 16 + rows * 4 + rows * ((gpr * 5 + 7) / 8);
+        }
+        default: return 0;
+    }
+}
+
+static std::atomic<uint64_t> g_next_uid{1};
+
+template <class T> static T rd(const uint8_t* p) {
+    T v;
+    memcpy(&v, p, sizeof(T));
+    return v;
+}
+
+int model_open(const char* path, Model** out) {
+    if (!path || !out) return fail(ERR_BAD_ARG, "model_open: null argument");
+    int fd = open(path, O_RDONLY);
+    if (fd < 0) return fail(ERR_IO, std::string("cannot open ") + path);
+    struct stat st;
+    if (fstat(fd, &st) != 0 || st.st_size < 128) {
+        close(fd);
+        return fail(ERR_FORMAT, std::string(path) + ": shorter than the 128-byte envelope");
+    }
+    void* mp = mmap(nullptr, (size_t)st.st_size, PROT_READ, MAP_PRIVATE, fd, 0);
+    close(fd);
+    if (mp == MAP_FAILED) return fail(ERR_IO, std::string("mmap failed for ") + path);
+    const uint8_t* b = reinterpret_cast<const uint8_t*>(mp);
+    const size_t len = (size_t)st.st_size;
+    auto bad = [&](const std::string& why) {
+        munmap(mp, len);
+        return fail(ERR_FORMAT, std::string(path) + ": " + why);
+    };
+    if (memcmp(b, "CMF\x01", 4) != 0) return bad("bad magic");
+    if (rd<uint32_t>(b + 4) != 2) return bad("unsupported container version");
+    const uint32_t required = rd<uint32_t>(b + 12);
+    if (required & ~0x7u) return bad("unknown required feature bits");
+    const uint64_t hdr_off = rd<uint64_t>(b + 0x10), hdr_len = rd<uint64_t>(b + 0x18);
+    const uint64_t dir_off = rd<uint64_t>(b + 0x20), dir_len = rd<uint64_t>(b + 0x28);
+    const uint64_t data_off = rd<uint64_t>(b + 0x30), data_len = rd<uint64_t>(b + 0x38);
+    if (hdr_off + hdr_len > len || dir_off + dir_len > len || data_off + data_len > len || dir_len < 16)
+        return bad("section outside the file");
+    if (data_off % 4096) return bad("data section is not 4096-aligned");
+    if (rd<uint64_t>(b + 0x70) != hash64(b + hdr_off, hdr_len)) return bad("header hash mismatch");
+    const uint64_t dir_hash = rd<uint64_t>(b + 0x78);
+    if (dir_hash && dir_hash != hash64(b + dir_off, dir_len)) return bad("directory hash mismatch");
+    const uint8_t* d = b + dir_off;
+    const uint64_t count = rd<uint64_t>(d), pool_off = rd<uint64_t>(d + 8);
+    if (16 + count * 56 > dir_len || pool_off > dir_len) return bad("directory records overrun the section");
+    std::unique_ptr<Model> m(new Model());
+    m->uid = g_next_uid++;
+    m->path = path;
+    m->map = b;
+    m->map_len = len;
+    m->data_off = data_off;
+    m->recs.resize(count);
+    for (uint64_t i = 0; i < count; ++i) {
+        const uint8_t* r = d + 16 + i * 56;
+        TensorRec& t = m->recs[i];
+        const uint32_t noff = rd<uint32_t>(r);
+        const uint16_t nlen = rd<uint16_t>(r + 4);
+        t.dtype = r[6];
+        t.ndim = r[7];
+        if (t.ndim > 6) return bad("tensor rank above 6");
+        for (int k = 0; k < 6; ++k) t.shape[k] = rd<uint32_t>(r + 8 + 4 * k);
+        t.off = rd<uint64_t>(r + 32);
+        t.nbytes = rd<uint64_t>(r + 40);
+        t.hash = rd<uint64_t>(r + 48);
+        if (pool_off + noff + nlen > dir_len) return bad("tensor name outside the name pool");
+        t.name.assign(reinterpret_cast<const char*>(d + pool_off + noff), nlen);
+        if (t.off % 64) return bad("tensor " + t.name + " is not 64-byte aligned");
+        if (t.off + t.nbytes > data_len) return bad("tensor " + t.name + " runs past the data section");
+        if (t.ndim == 2) {
+            size_t want = payload_nbytes(t.dtype, t.shape[0], t.shape[1]);
+            if (want && want != t.nbytes) return bad("tensor " + t.name + ": byte count disagrees with dtype and shape");
+        }
+        m->by_name[t.name] = (int64_t)i;
+    }
+    *out = m.release();
+    return OK;
+}
+
+void model_close(Model* m) {
+    if (!m) return;
+    {
+        std::lock_guard<std::mutex> lk(g_ctx_mu);
+        for (auto& kv : g_ctxs) {
+            Context* c = kv.second.get();
+            cudaSetDevice(c->device);
+            cudaStreamSynchronize(c->stream);
+            for (auto it = c->weights.begin(); it != c->weights.end();) {
+                if (std::get<0>(it->first) == m->uid) {
+                    if (it->second->owns) {
+                        cudaFree(it->second->plane);
+                        cudaFree(it->second->scales);
+                    }
+                    it = c->weights.erase(it);
+                } else {
+                    ++it;
+                }
+            }
+        }
+    }
+    munmap(const_cast<uint8_t*>(m->map), m->map_len);
+    delete m;
+}
+
+// ---------------- weights ----------------
+static uint16_t rd16(const uint8_t* p) { return (uint16_t)(p[0] | (p[1] << 8)); }
+static float half_to_float_host(uint16_t h) {
+    uint32_t s = (uint32_t)(h >> 15) << 31, e = (h >> 10) & 0x1F, m = h & 0x3FF, bits;
+    if (e == 0) {
+        if (!m) bits = s;
+        else {
+            uint32_t sh = 0;
+            while (!(m & 0x400)) { m <<= 1; ++sh; }
+            bits = s | ((113 - sh) << 23) | ((m & 0x3FF) << 13);
+        }
+    } else if (e == 0x1F) bits = s | 0x7F800000u | (m << 13);
+    else bits = s | ((e + 112) << 23) | (m << 13);
+    float f;
+    memcpy(&f, &bits, 4);
+    return f;
+}
+
+static int finish_gemm_maps(DevWeight* w) {
+    if (w->dtype == DT_F32) return OK;
+    if (w->rows % 128 || w->cols % 64) return OK;  // usable by gemv / dequant only
+    if (w->dtype == DT_Q8) {
+        CMFC_TRY(make_tensor_map_2d(&w->tm_w, w->plane, 1, w->rows, w->cols, w->cols, 128, 64, 2));
+        w->tm_s = w->tm_w;
+    } else {
+        CMFC_TRY(make_tensor_map_2d(&w->tm_w, w->plane, 1, w->rows, w->cols / 2, w->cols / 2, 128, 32, 1));
+        CMFC_TRY(make_tensor_map_2d(&w->tm_s, w->scales, 4, w->cols / 32, w->rows, (uint64_t)w->rows * 4, 2, 128, 0));
+    }
+    w->gemm_ready = true;
+    return OK;
+}
+
+static int alloc_planes(DevWeight* w) {
+    size_t plane_b, scale_b;
+    if (w->dtype == DT_Q8) { plane_b = (size_t)w->rows * w->cols; scale_b = (size_t)w->rows * 4; }
+    else if (w->is_q4()) { plane_b = (size_t)w->rows * w->cols / 2; scale_b = (size_t)w->rows * (w->cols / 32) * 4; }
+    else { plane_b = (size_t)w->rows * w->cols * 4; scale_b = 0; }
+    if (cudaMalloc(&w->plane, plane_b) != cudaSuccess) return fail(ERR_OOM, "out of device memory for a weight plane");
+    if (scale_b && cudaMalloc(&w->scales, scale_b) != cudaSuccess) return fail(ERR_OOM, "out of device memory for weight scales");
+    w->bytes = plane_b + scale_b;
+    return OK;
+}
+
+int get_weight(Context* c, Model* m, int64_t idx, DevWeight** out) {
+    if (!m || idx < 0 || idx >= (int64_t)m->recs.size()) return fail(ERR_BAD_ARG, "tensor index out of range");
+    auto key = std::make_tuple(m->uid, idx, (int64_t)-1, (int64_t)-1, 0);
+    auto it = c->weights.find(key);
+    if (it != c->weights.end()) { *out = it->second.get(); return OK; }
+    const TensorRec& t = m->recs[idx];
+    if (t.ndim != 2) return fail(ERR_SHAPE, "tensor " + t.name + " is not 2-D");
+    if (t.dtype != DT_Q8 && t.dtype != DT_Q4T && t.dtype != DT_Q4TP)
+        return fail(ERR_UNSUPPORTED, "tensor " + t.name + ": dtype " + std::to_string(t.dtype) + " is not q8_row / q4_tiled / q4tp");
+    const int rows = (int)t.shape[0], cols = (int)t.shape[1];
+    if (t.dtype != DT_Q8 && cols % 32) return fail(ERR_SHAPE, "tensor " + t.name + ": 4-bit codecs need cols % 32 == 0");
+    if (cols % 16) return fail(ERR_SHAPE, "tensor " + t.name + ": cols must be a multiple of 16");
+    std::unique_ptr<DevWeight> w(new DevWeight());
+    w->dtype = t.dtype; w->rows = rows; w->cols = cols;
+    CMFC_TRY(alloc_planes(w.get()));
+    const uint8_t* src = m->bytes(idx);
+    cudaStream_t s = c->stream;
+    if (t.dtype == DT_Q8) {
+        CMFC_CUDA(cudaMemcpyAsync(w->plane, src, (size_t)rows * cols, cudaMemcpyHostToDevice, s));
+        std::vector<float> sc(rows);
+        for (int r = 0; r < rows; ++r) sc[r] = half_to_float_host(rd16(src + (size_t)rows * cols + 2 * r));
+        CMFC_CUDA(cudaMemcpyAsync(w->scales, sc.data(), (size_t)rows * 4, cudaMemcpyHostToDevice, s));
+        CMFC_CUDA(cudaStreamSynchronize(s));
+    } else if (t.dtype == DT_Q4T) {
+        DevBuf& raw = c->buf("upload_raw");
+        CMFC_TRY(raw.ensure(t.nbytes));
+        CMFC_CUDA(cudaMemcpyAsync(raw.p, src, t.nbytes, cudaMemcpyHostToDevice, s));
+        launch_q4t_split(raw.as<uint8_t>(), rows, cols, w->plane, w->scales, s);
+        c->launches++;
+        CMFC_CUDA(cudaStreamSynchronize(s));
+    } else {
+        const int gpr = cols / 32, stride = (gpr * 5 + 7) / 8;
+        const size_t nib_b = (size_t)rows * gpr * 16;
+        CMFC_CUDA(cudaMemcpyAsync(w->plane, src, nib_b, cudaMemcpyHostToDevice, s));
+        // Ladders on the host, with the host's exp2f, iterated exactly as the format defines
+        // (crates/cortiq-core/src/quant.rs:396-411).
+        std::vector<float> lad((size_t)rows * 32);
+        const uint8_t* params = src + nib_b;
+        for (int r = 0; r < rows; ++r) {
+            const float lo = half_to_float_host(rd16(params + 4 * r)), st = half_to_float_host(rd16(params + 4 * r + 2));
+            const float ratio = exp2f(st);
+            float tv = exp2f(lo);
+            lad[(size_t)r * 32] = tv;
+            for (int k = 1; k < 32; ++k) {
+                volatile float nx = tv * ratio;  // plain IEEE multiply, never contracted
+                tv = nx;
+                lad[(size_t)r * 32 + k] = tv;
+            }
+        }
+        DevBuf& raw = c->buf("upload_raw");
+        const size_t codes_b = (size_t)rows * stride, lad_b = lad.size() * 4;
+        CMFC_TRY(raw.ensure(((codes_b + 255) & ~size_t(255)) + lad_b));
+        uint8_t* d_codes = raw.as<uint8_t>();
+        float* d_lad = reinterpret_cast<float*>(d_codes + ((codes_b + 255) & ~size_t(255)));
+        CMFC_CUDA(cudaMemcpyAsync(d_codes, params + (size_t)rows * 4, codes_b, cudaMemcpyHostToDevice, s));
+        CMFC_CUDA(cudaMemcpyAsync(d_lad, lad.data(), lad_b, cudaMemcpyHostToDevice, s));
+        launch_q4tp_scales(d_codes, stride, d_lad, rows, gpr, w->scales, s);
+        c->launches++;
+        CMFC_CUDA(cudaStreamSynchronize(s));
+    }
+    CMFC_CUDA(cudaGetLastError());
+    CMFC_TRY(finish_gemm_maps(w.get()));
+    *out = w.get();
+    c->weights[key] = std::move(w);
+    return OK;
+}
+
+int upload_f32(Context* c, Model* m, int64_t idx, DevWeight** out) {
+    if (!m || idx < 0 || idx >= (int64_t)m->recs.size()) return fail(ERR_BAD_ARG, "tensor index out of range");
+    auto key = std::make_tuple(m->uid, idx, (int64_t)-1, (int64_t)-1, 9);
+    auto it = c->weights.find(key);
+    if (it != c->weights.end()) { *out = it->second.get(); return OK; }
+    const TensorRec& t = m->recs[idx];
+    size_t n = 1;
+    for (int k = 0; k < t.ndim; ++k) n *= t.shape[k];
+    std::unique_ptr<DevWeight> w(new DevWeight());
+    w->dtype = DT_F32;
+    w->rows = t.ndim == 2 ? (int)t.shape[0] : 1;
+    w->cols = (int)(n / w->rows);
+    if (cudaMalloc(&w->plane, n * 4) != cudaSuccess) return fail(ERR_OOM, "out of device memory for tensor " + t.name);
+    w->bytes = n * 4;
+    const uint8_t* src = m->bytes(idx);
+    if (t.dtype == DT_F32) {
+        if (t.nbytes != n * 4) return fail(ERR_SHAPE, "tensor " + t.name + ": byte count disagrees with shape");
+        CMFC_CUDA(cudaMemcpy(w->plane, src, n * 4, cudaMemcpyHostToDevice));
+    } else if (t.dtype == DT_F16) {
+        std::vector<float> tmp(n);
+        for (size_t i = 0; i < n; ++i) tmp[i] = half_to_float_host(rd16(src + 2 * i));
+        CMFC_CUDA(cudaMemcpy(w->plane, tmp.data(), n * 4, cudaMemcpyHostToDevice));
+    } else {
+        return fail(ERR_UNSUPPORTED, "tensor " + t.name + ": expected f32 or f16, found dtype " + std::to_string(t.dtype));
+    }
+    *out = w.get();
+    c->weights[key] = std::move(w);
+    return OK;
+}
+
+// rows of a | b | cc stacked (all same dtype family and cols)
+int get_weight_concat(Context* c, Model* m, int64_t a, int64_t b, int64_t cc, DevWeight** out) {
+    auto key = std::make_tuple(m->uid, a, b, cc, 1);
+    auto it = c->weights.find(key);
+    if (it != c->weights.end()) { *out = it->second.get(); return OK; }
+    DevWeight* parts[3] = {nullptr, nullptr, nullptr};
+    CMFC_TRY(get_weight(c, m, a, &parts[0]));
+    CMFC_TRY(get_weight(c, m, b, &parts[1]));
+    CMFC_TRY(get_weight(c, m, cc, &parts[2]));
+    const bool q4 = parts[0]->is_q4();
+    int rows = 0;
+    for (auto* p : parts) {
+        if (p->cols != parts[0]->cols || p->is_q4() != q4 || (!q4 && p->dtype != DT_Q8))
+            return fail(ERR_UNSUPPORTED, "fused projection needs one codec family and one input width");
+        rows += p->rows;
+    }
+    std::unique_ptr<DevWeight> w(new DevWeight());
+    w->dtype = q4 ? DT_Q4T : DT_Q8;  // q4t and q4tp share planes once uploaded
+    w->rows = rows; w->cols = parts[0]->cols;
+    CMFC_TRY(alloc_planes(w.get()));
+    const size_t row_b = q4 ? w->cols / 2 : w->cols;
+    size_t r0 = 0;
+    for (auto* p : parts) {
+        CMFC_CUDA(cudaMemcpyAsync(w->plane + r0 * row_b, p->plane, (size_t)p->rows * row_b, cudaMemcpyDeviceToDevice, c->stream));
+        if (q4) {  // transposed scales [gpr, rows]: a column block per part
+            CMFC_CUDA(cudaMemcpy2DAsync(w->scales + r0, (size_t)rows * 4, p->scales, (size_t)p->rows * 4, (size_t)p->rows * 4,
+                                        w->cols / 32, cudaMemcpyDeviceToDevice, c->stream));
+        } else {
+            CMFC_CUDA(cudaMemcpyAsync(w->scales + r0, p->scales, (size_t)p->rows * 4, cudaMemcpyDeviceToDevice, c->stream));
+        }
+        r0 += p->rows;
+    }
+    CMFC_CUDA(cudaStreamSynchronize(c->stream));
+    CMFC_TRY(finish_gemm_maps(w.get()));
+    *out = w.get();
+    c->weights[key] = std::move(w);
+    return OK;
+}
+
+// rows alternate a[0], b[0], a[1], b[1], ... (gate / up of SwiGLU side by side in one tile)
+int get_weight_interleaved(Context* c, Model* m, int64_t a, int64_t b, DevWeight** out) {
+    auto key = std::make_tuple(m->uid, a, b, (int64_t)-1, 2);
+    auto it = c->weights.find(key);
+    if (it != c->weights.end()) { *out = it->second.get(); return OK; }
+    DevWeight *pa = nullptr, *pb = nullptr;
+    CMFC_TRY(get_weight(c, m, a, &pa));
+    CMFC_TRY(get_weight(c, m, b, &pb));
+    if (pa->rows != pb->rows || pa->cols != pb->cols || pa->is_q4() != pb->is_q4())
+        return fail(ERR_UNSUPPORTED, "SwiGLU gate and up projections must share shape and codec family");
+    const bool q4 = pa->is_q4();
+    std::unique_ptr<DevWeight> w(new DevWeight());
+    w->dtype = q4 ? DT_Q4T : DT_Q8;
+    w->rows = 2 * pa->rows; w->cols = pa->cols;
+    CMFC_TRY(alloc_planes(w.get()));
+    const size_t row_b = q4 ? w->cols / 2 : w->cols;
+    DevWeight* parts[2] = {pa, pb};
+    for (int k = 0; k < 2; ++k) {
+        CMFC_CUDA(cudaMemcpy2DAsync(w->plane + k * row_b, 2 * row_b, parts[k]->plane, row_b, row_b, pa->rows,
+                                    cudaMemcpyDeviceToDevice, c->stream));
+        // scales: q8 [rows] -> stride 2 floats; q4 transposed [gpr, rows] -> every row of the
+        // plane is itself interleaved, which is the same 4-byte element copy with pitch 8.
+        const size_t count = q4 ? (size_t)pa->rows * (w->cols / 32) : (size_t)pa->rows;
+        launch_interleave_f32(w->scales, 2, k, parts[k]->scales, count, c->stream);
+    }
+    CMFC_CUDA(cudaStreamSynchronize(c->stream));
+    CMFC_TRY(finish_gemm_maps(w.get()));
+    *out = w.get();
+    c->weights[key] = std::move(w);
+    return OK;
+}
+
+// ---------------- device-level ops ----------------
+int dev_gemm(Context* c, DevWeight* w, const __nv_bfloat16* x, int M, void* out, int ldo, int mode) {
+    if (!w->gemm_ready)
+        return fail(ERR_SHAPE, "dequant GEMM needs rows % 128 == 0 and cols % 64 == 0 (got " + std::to_string(w->rows) +
+                                   " x " + std::to_string(w->cols) + ")");
+    CUtensorMap tm_x;
+    CMFC_TRY(make_tensor_map_2d(&tm_x, x, 2, (uint64_t)M, (uint64_t)w->cols, (uint64_t)w->cols * 2, 256, 64, 3));
+    GemmParams p;
+    p.M = M; p.N = w->rows; p.K = w->cols;
+    p.out = out; p.ldo = ldo; p.mode = mode;
+    p.row_scale = w->dtype == DT_Q8 ? w->scales : nullptr;
+    p.status = c->status;
+    c->launches++;
+    return launch_gemm_dequant(w->dtype == DT_Q8 ? 0 : 1, tm_x, w->tm_w, w->tm_s, p, c->num_sms, c->stream);
+}
+
+// Segment table on the device: [nseg+1] token offsets, then [nseg] first V^T column of each
+// segment (8-aligned, so every TMA x coordinate is a multiple of 16 bytes).  Re-uploaded only
+// when the segmentation changes.
+int prepare_segs(Context* c, const std::vector<int>& segs, SegTable* out) {
+    SegTable& st = c->segs;
+    if (st.host != segs || !st.dev) {
+        std::vector<int> tab(2 * segs.size() + 1, 0);
+        int mx = 0, col = 0;
+        for (size_t i = 0; i < segs.size(); ++i) {
+            if (segs[i] <= 0) return fail(ERR_BAD_ARG, "empty segment");
+            tab[i + 1] = tab[i] + segs[i];
+            tab[segs.size() + 1 + i] = col;
+            col += (segs[i] + 7) & ~7;
+            mx = segs[i] > mx ? segs[i] : mx;
+        }
+        DevBuf& sb = c->buf("seg_table");
+        CMFC_TRY(sb.ensure(tab.size() * 4));
+        CMFC_CUDA(cudaMemcpyAsync(sb.p, tab.data(), tab.size() * 4, cudaMemcpyHostToDevice, c->stream));
+        CMFC_CUDA(cudaStreamSynchronize(c->stream));  // tab is a stack temporary
+        st.host = segs;
+        st.dev = sb.as<int>();
+        st.n_total = tab[segs.size()];
+        st.vt_pitch = col;
+        st.max_seg = mx;
+    }
+    *out = st;
+    return OK;
+}
+
+int dev_attention(Context* c, const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* vt,
+                  const SegTable& st, int nh, int nkv, int hd, float scale, __nv_bfloat16* out) {
+    if (hd % 32 || hd > 128 || hd < 32) return fail(ERR_UNSUPPORTED, "attention needs head_dim in {32, 64, 96, 128}");
+    if (nh % nkv) return fail(ERR_BAD_ARG, "query heads must be a multiple of kv heads");
+    CUtensorMap tm_q, tm_k, tm_vt;
+    // Q / K: [n_total, heads*hd] bf16, boxes of 128 tokens x 32 dims, 64-byte swizzle
+    CMFC_TRY(make_tensor_map_2d(&tm_q, q, 2, st.n_total, (uint64_t)nh * hd, (uint64_t)nh * hd * 2, 128, 32, 2));
+    CMFC_TRY(make_tensor_map_2d(&tm_k, k, 2, st.n_total, (uint64_t)nkv * hd, (uint64_t)nkv * hd * 2, 128, 32, 2));
+    // V^T: [nkv*hd, vt_pitch] bf16, boxes of hd rows x 64 keys, 128-byte swizzle
+    CMFC_TRY(make_tensor_map_2d(&tm_vt, vt, 2, (uint64_t)nkv * hd, (uint64_t)st.vt_pitch, (uint64_t)st.vt_pitch * 2, hd, 64, 3));
+    AttnParams p;
+    p.nh = nh; p.nkv = nkv; p.hd = hd; p.n_total = st.n_total; p.vt_pitch = st.vt_pitch;
+    p.seg_start = st.dev; p.nseg = (int)st.host.size(); p.max_seg = st.max_seg; p.scale = scale;
+    p.out = out; p.status = c->status;
+    c->launches++;
+    return launch_attention(tm_q, tm_k, tm_vt, p, c->stream);
+}
+
+int dev_block(Context* c, const BlockWeights& bw, const BlockMod& mod, float* x, int n, const std::vector<int>& segs,
+              int hidden, int inter, int nh, int nkv, int hd, double eps, const double* cos_t, const double* sin_t) {
+    cudaStream_t s = c->stream;
+    const int qkv_w = (nh + 2 * nkv) * hd;
+    SegTable st;
+    CMFC_TRY(prepare_segs(c, segs, &st));
+    if (st.n_total != n) return fail(ERR_BAD_ARG, "segments do not sum to the token count");
+    const int vt_pitch = st.vt_pitch;
+    if (!row_cols_supported(hidden)) return fail(ERR_UNSUPPORTED, "hidden size " + std::to_string(hidden) + " is not supported by the row kernels");
+    DevBuf &xn = c->buf("blk_xn"), &qkv = c->buf("blk_qkv"), &qb = c->buf("blk_q"), &kb = c->buf("blk_k"),
+           &vt = c->buf("blk_vt"), &att = c->buf("blk_attn"), &proj = c->buf("blk_proj"), &act = c->buf("blk_act");
+    CMFC_TRY(xn.ensure((size_t)n * hidden * 2));
+    CMFC_TRY(qkv.ensure((size_t)n * qkv_w * 4));
+    CMFC_TRY(qb.ensure((size_t)n * nh * hd * 2));
+    CMFC_TRY(kb.ensure((size_t)n * nkv * hd * 2));
+    if (vt.cap < (size_t)nkv * hd * vt_pitch * 2) {
+        CMFC_TRY(vt.ensure((size_t)nkv * hd * vt_pitch * 2));
+        CMFC_CUDA(cudaMemsetAsync(vt.p, 0, vt.cap, s));  // pad columns must hold finite values
+    }
+    CMFC_TRY(att.ensure((size_t)n * nh * hd * 2));
+    CMFC_TRY(proj.ensure((size_t)n * hidden * 4));
+    CMFC_TRY(act.ensure((size_t)n * inter * 2));
+    {
+        SpanGuard g(c, "mod-norm");
+        launch_rms_mod(x, bw.norm1, mod.s_msa, eps, n, hidden, xn.as<__nv_bfloat16>(), nullptr, s);
+        c->launches++;
+    }
+    {
+        SpanGuard g(c, "qkv-proj");
+        CMFC_TRY(dev_gemm(c, bw.qkv, xn.as<__nv_bfloat16>(), n, qkv.p, qkv_w, GEMM_OUT_F32));
+    }
+    {
+        SpanGuard g(c, "rope");
+        launch_qk_rope_pack(qkv.as<float>(), n, nh, nkv, hd, bw.norm_q, bw.norm_k, cos_t, sin_t, qb.as<__nv_bfloat16>(),
+                            kb.as<__nv_bfloat16>(), vt.as<__nv_bfloat16>(), vt_pitch, st.dev, (int)segs.size(), st.max_seg, s);
+        c->launches += 2;
+    }
+    {
+        SpanGuard g(c, "attention");
+        CMFC_TRY(dev_attention(c, qb.as<__nv_bfloat16>(), kb.as<__nv_bfloat16>(), vt.as<__nv_bfloat16>(), st, nh, nkv, hd,
+                               1.0f / sqrtf((float)hd), att.as<__nv_bfloat16>()));
+    }
+    {
+        SpanGuard g(c, "o-proj");
+        CMFC_TRY(dev_gemm(c, bw.o, att.as<__nv_bfloat16>(), n, proj.p, hidden, GEMM_OUT_F32));
+    }
+    {
+        SpanGuard g(c, "mod-norm");
+        // x += gate_msa * rms(proj; norm2); xn = rms(x; ffn_norm1) * (1 + s_mlp)
+        launch_residual_then_norm(x, proj.as<float>(), bw.norm2, mod.gate_msa, bw.ffn_norm1, mod.s_mlp, eps, n, hidden,
+                                  xn.as<__nv_bfloat16>(), s);
+        c->launches++;
+    }
+    {
+        SpanGuard g(c, "ffn-mm");
+        CMFC_TRY(dev_gemm(c, bw.w13, xn.as<__nv_bfloat16>(), n, act.p, inter, GEMM_OUT_SWIGLU));
+        CMFC_TRY(dev_gemm(c, bw.w2, act.as<__nv_bfloat16>(), n, proj.p, hidden, GEMM_OUT_F32));
+    }
+    {
+        SpanGuard g(c, "mod-norm");
+        launch_gated_residual(x, proj.as<float>(), bw.ffn_norm2, mod.gate_mlp, eps, n, hidden, s);
+        c->launches++;
+    }
+    CMFC_CUDA(cudaGetLastError());
+    return OK;
+}
+
+}  // namespace cmfc

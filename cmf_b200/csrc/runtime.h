@@ -1,0 +1,131 @@
+// Host runtime behind the C ABI: per-device context (stream, workspaces, weight cache),
+// the memory-mapped container, device weights and the device-level ops composed from kernels.
+#pragma once
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <tuple>
+#include <vector>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace cmfc {
+
+enum : int { DT_F32 = 0, DT_F16 = 1, DT_U8 = 6, DT_Q8 = 3, DT_Q4T = 11, DT_Q4TP = 15 };
+
+// ---- growable device buffer (no allocation in steady state) ----
+struct DevBuf {
+    void* p = nullptr;
+    size_t cap = 0;
+    int ensure(size_t bytes);
+    void release();
+    template <class T> T* as() const { return reinterpret_cast<T*>(p); }
+};
+
+// ---- container (crates/cortiq-core/src/format.rs: envelope, directory) ----
+struct TensorRec {
+    std::string name;
+    int dtype = 0, ndim = 0;
+    uint32_t shape[6] = {0, 0, 0, 0, 0, 0};
+    uint64_t off = 0, nbytes = 0, hash = 0;
+};
+struct Model {
+    uint64_t uid = 0;
+    std::string path;
+    const uint8_t* map = nullptr;
+    size_t map_len = 0;
+    uint64_t data_off = 0;
+    std::vector<TensorRec> recs;
+    std::map<std::string, int64_t> by_name;
+    const uint8_t* bytes(int64_t idx) const { return map + data_off + recs[idx].off; }
+};
+int model_open(const char* path, Model** out);
+void model_close(Model* m);
+uint64_t hash64(const uint8_t* p, size_t n);
+size_t payload_nbytes(int dtype, size_t rows, size_t cols);
+
+// ---- a weight resident on the device, in the planes the kernels read ----
+struct DevWeight {
+    int dtype = 0;         // DT_Q8 / DT_Q4T / DT_Q4TP / DT_F32
+    int rows = 0, cols = 0;
+    uint8_t* plane = nullptr;   // q8: int8 [rows, cols]; q4: nibbles [rows, cols/2]; f32: dense
+    float* scales = nullptr;    // q8: row scales [rows]; q4: transposed group scales [cols/32, rows]
+    CUtensorMap tm_w, tm_s;     // TMA descriptors of the planes (valid when gemm_ready)
+    bool gemm_ready = false;
+    bool owns = true;
+    size_t bytes = 0;
+    bool is_q4() const { return dtype == DT_Q4T || dtype == DT_Q4TP; }
+};
+
+struct SegTable {
+    std::vector<int> host;  // segment lengths
+    const int* dev = nullptr;  // [nseg+1] token offsets, then [nseg] V^T column offsets
+    int n_total = 0, vt_pitch = 0, max_seg = 0;
+};
+
+struct Profile {
+    bool on = false;
+    std::vector<std::pair<std::string, std::pair<cudaEvent_t, cudaEvent_t>>> spans;
+};
+
+struct Context {
+    int device = -1;
+    cudaStream_t stream = nullptr;
+    int num_sms = 0;
+    uint32_t* status = nullptr;       // device status word for bounded-wait kernels
+    uint32_t* status_host = nullptr;  // pinned mirror
+    std::map<std::tuple<uint64_t, int64_t, int64_t, int64_t, int>, std::unique_ptr<DevWeight>> weights;
+    std::map<std::string, DevBuf> ws;  // named workspaces
+    SegTable segs;
+    DevBuf resident_x;                 // hidden state kept between chained dit_block_seg calls
+    size_t resident_len = 0;
+    float* log2_lut = nullptr;         // [65536] log2f of every f16 value (host libm)
+    float* exp2_lut = nullptr;         // [65536] exp2f of every f16 value
+    uint64_t launches = 0;
+    Profile prof;
+    DevBuf& buf(const std::string& name) { return ws[name]; }
+};
+
+const std::string& last_error();
+Context* ctx();  // context of the calling thread's current device (created on demand), or null
+int ctx_set_device(int device);
+int check_status(Context* c, const char* what);  // reads the device status word (after a sync)
+
+// weights
+int get_weight(Context* c, Model* m, int64_t idx, DevWeight** out);
+// concatenation along rows of up to three tensors (qkv), or row-interleave of two (w1/w3)
+int get_weight_concat(Context* c, Model* m, int64_t a, int64_t b, int64_t cc, DevWeight** out);
+int get_weight_interleaved(Context* c, Model* m, int64_t a, int64_t b, DevWeight** out);
+int upload_f32(Context* c, Model* m, int64_t idx, DevWeight** out);  // any float tensor -> dense f32
+
+// device-level ops (device pointers; async on c->stream)
+int dev_gemm(Context* c, DevWeight* w, const __nv_bfloat16* x, int M, void* out, int ldo, int mode);
+int prepare_segs(Context* c, const std::vector<int>& segs, SegTable* out);
+int dev_attention(Context* c, const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* vt,
+                  const SegTable& st, int nh, int nkv, int hd, float scale, __nv_bfloat16* out);
+
+struct BlockWeights {
+    DevWeight *qkv = nullptr, *o = nullptr, *w13 = nullptr, *w2 = nullptr;
+    const float *norm1 = nullptr, *norm2 = nullptr, *ffn_norm1 = nullptr, *ffn_norm2 = nullptr;
+    const float *norm_q = nullptr, *norm_k = nullptr;
+};
+struct BlockMod {  // all null for an unmodulated block; gates already tanh'd
+    const float *s_msa = nullptr, *gate_msa = nullptr, *s_mlp = nullptr, *gate_mlp = nullptr;
+};
+// One block over x [n, hidden] f32 in place (crates/cortiq-engine/src/dit.rs:943-1177).
+int dev_block(Context* c, const BlockWeights& bw, const BlockMod& mod, float* x, int n, const std::vector<int>& segs,
+              int hidden, int inter, int nh, int nkv, int hd, double eps, const double* cos_t, const double* sin_t);
+
+bool row_cols_supported(int cols);
+void launch_gemv_silu2(const GemvParams& p, float* y_silu, cudaStream_t s);
+
+struct SpanGuard {
+    Context* c;
+    size_t idx = (size_t)-1;
+    SpanGuard(Context* c, const char* name);
+    ~SpanGuard();
+};
+
+}  // namespace cmfc

@@ -1,0 +1,191 @@
+/*
+ * libcmf_cuda -- B200 (sm_100a) compute backend for the NextDiT denoiser path of the CMF
+ * engine.  Plain C ABI: pointers and sizes only.  Every entry returns 0 on success or a
+ * negative status; cmfc_last_error() gives the thread's last message.  Nothing throws or
+ * aborts across this boundary, and nothing falls back to the CPU: an entry either ran on the
+ * device or failed with a status.
+ *
+ * Each entry names the reference interface it replaces (paths relative to the reference
+ * repository; `gpu.rs` is crates/cortiq-engine/src/gpu.rs, the engine's backend facade).
+ *
+ * Host pointers are borrowed for the duration of the call.  Weight bytes are copied to the
+ * device once per (model, directory index) and owned by the library until cmfc_model_close.
+ * Calls on one device context are serialized by the caller (the engine drives a denoise from
+ * one thread); the current device is selected per thread with cmfc_set_device.
+ */
+#ifndef CMF_CUDA_H
+#define CMF_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* status codes */
+#define CMFC_OK 0
+#define CMFC_ERR_BAD_ARG (-1)      /* null pointer, zero size, segs not summing to n ... */
+#define CMFC_ERR_UNSUPPORTED (-2)  /* dtype or geometry this backend does not implement */
+#define CMFC_ERR_SHAPE (-3)        /* shape disagrees with the tensor's directory record */
+#define CMFC_ERR_OOM (-4)
+#define CMFC_ERR_DEVICE_WAIT (-5)  /* a kernel ran out of its bounded wait budget */
+#define CMFC_ERR_CUDA (-6)
+#define CMFC_ERR_IO (-7)
+#define CMFC_ERR_FORMAT (-8)       /* container validation failed */
+#define CMFC_ERR_NOT_FOUND (-9)
+
+/* TensorDtype ids of the container (crates/cortiq-core/src/types.rs:10-98) */
+#define CMFC_DT_F32 0
+#define CMFC_DT_F16 1
+#define CMFC_DT_U8 6
+#define CMFC_DT_Q8_ROW 3
+#define CMFC_DT_Q4_TILED 11
+#define CMFC_DT_Q4TP 15
+
+typedef struct cmfc_model cmfc_model;     /* an opened, memory-mapped .cmf container */
+typedef struct cmfc_nextdit cmfc_nextdit; /* a NextDiT bound to a model, weights resident */
+
+/* Thread-local message of the last failing call on this thread
+ * (style of crates/cortiq-ffi/include/cortiq.h:5-7, cortiq_last_error). */
+const char* cmfc_last_error(void);
+
+/* ---- devices: gpu.rs:962-1013 device_count / set_current_device / with_device ---- */
+int cmfc_device_count(void);
+int cmfc_set_device(int device); /* creates the device context on first use */
+int cmfc_synchronize(void);
+
+/* ---- container: crates/cortiq-core/src/format.rs:390-584 CmfModel::open (envelope :653-728,
+ * directory :730-791).  The file is mmap'ed; tensors are uploaded on first use. ---- */
+int cmfc_model_open(const char* path, cmfc_model** out);
+void cmfc_model_close(cmfc_model* m);
+int64_t cmfc_model_tensor_count(const cmfc_model* m);
+/* directory index of `name`, or CMFC_ERR_NOT_FOUND  (format.rs CmfModel::tensor) */
+int64_t cmfc_model_find(const cmfc_model* m, const char* name);
+/* directory record idx -> dtype id, ndim, shape[6], payload bytes */
+int cmfc_model_tensor_info(const cmfc_model* m, int64_t idx, int* dtype, int* ndim, uint32_t shape[6],
+                           uint64_t* nbytes);
+/* pointer into the mapping (valid until close) */
+const void* cmfc_model_tensor_bytes(const cmfc_model* m, int64_t idx);
+
+/* gpu.rs:507 weight_is_resident */
+int cmfc_weight_is_resident(const cmfc_model* m, int64_t idx);
+/* Exact f32 dequantization of tensor idx ON THE DEVICE from the planes the GEMM reads,
+ * copied to `out` [rows*cols] -- the bit-exactness check against
+ * crates/cortiq-core/src/quant.rs:91-103 / :322-344 / :413-431. */
+int cmfc_weight_dequant(cmfc_model* m, int64_t idx, float* out, size_t out_len);
+
+/* ---- quantized linears: Y[b, rows] = X[b, cols] . W^T, host f32 in / out.
+ * gpu.rs:1155 q8_matmat, :2358 q4t_matmat, :2439 q4tp_matmat (called from
+ * crates/cortiq-engine/src/qtensor.rs:1483-1584, :1637-1710, :1806-1858). ---- */
+int cmfc_q8_matmat(cmfc_model* m, int64_t idx, const float* xs, size_t b, size_t rows, size_t cols, float* out);
+int cmfc_q4t_matmat(cmfc_model* m, int64_t idx, const float* xs, size_t b, size_t rows, size_t cols, float* out);
+int cmfc_q4tp_matmat(cmfc_model* m, int64_t idx, const float* xs, size_t b, size_t rows, size_t cols, float* out);
+
+/* gpu.rs:1891 dit_qkv: three projections of one input in one submission */
+int cmfc_dit_qkv(cmfc_model* m, int64_t wq, int64_t wk, int64_t wv, const float* xs, size_t b, size_t hidden,
+                 size_t qrows, size_t kvrows, float* q_out, float* k_out, float* v_out);
+
+/* gpu.rs:1773-1813 q4t_ffn / q4tp_ffn: out = (silu(x W1^T) * (x W3^T)) W2^T; any of the three
+ * codecs is accepted for each projection */
+int cmfc_ffn(cmfc_model* m, int64_t w1, int64_t w3, int64_t w2, const float* xs, size_t b, size_t hidden,
+             size_t inter, float* out);
+
+/* gpu.rs:2332 dit_attention: q [nh][n][hd], k and v [nkv][n][hd] head-major f32 (q NOT yet
+ * scaled), out [n][nh*hd]; bidirectional softmax attention, GQA */
+int cmfc_dit_attention(const float* qh, const float* kh, const float* vh, size_t nh, size_t nkv, size_t n,
+                       size_t hd, float scale, float* out);
+
+/* gpu.rs:1819-1857 DitBlockArgs, field for field (slices become pointers; lengths are implied
+ * by n / hidden / hd as documented there; gates already tanh'd).  `codec` is informational:
+ * the library reads each projection's dtype from the directory and accepts q8 / q4t / q4tp in
+ * any mix. */
+typedef struct cmfc_dit_block_args {
+    uint32_t n, hidden, inter, nh, nkv, hd;
+    float eps;
+    const float* rope_cos; /* [n * hd/2] */
+    const float* rope_sin;
+    const float *norm1, *norm2, *ffn_norm1, *ffn_norm2; /* [hidden] */
+    const float *norm_q, *norm_k;                       /* [hd] */
+    const float *s_msa, *gate_msa, *s_mlp, *gate_mlp;   /* [hidden]; all four NULL = unmodulated block */
+    int64_t wq, wk, wv, wo, w1, w3, w2;                 /* directory indices */
+    int32_t q4tp;
+    int32_t resident_in;  /* hidden state is already on the device from the previous block */
+    int32_t resident_out; /* leave the result on the device */
+} cmfc_dit_block_args;
+
+/* gpu.rs:1936 dit_block_seg: one adaLN block over concatenated segments; x [n, hidden] in-out
+ * (ignored on the way in when resident_in, on the way out when resident_out) */
+int cmfc_dit_block_seg(cmfc_model* m, const cmfc_dit_block_args* a, const uint32_t* segs, size_t nseg, float* x);
+/* gpu.rs:1862 dit_chain_supported, :1873 dit_state_fetch, :1918 fused_dit_block_available */
+int cmfc_dit_chain_supported(void);
+int cmfc_dit_state_fetch(float* x, size_t len);
+int cmfc_fused_dit_block_available(void); /* 0: the batched CFG pair is the preferred shape */
+
+/* ---- whole forward / whole loop, device-resident (the graph of
+ * crates/cortiq-engine/src/dit.rs:1201-1507 and crates/cortiq-engine/src/imagegen.rs:143-217) ---- */
+
+/* NextDit::from_cmf (dit.rs:510-589): reads dit.config_json, resolves and uploads dit.* */
+int cmfc_nextdit_create(cmfc_model* m, cmfc_nextdit** out);
+void cmfc_nextdit_destroy(cmfc_nextdit* d);
+/* hidden_size, cap_feat, in_channels, patch_size, num_layers, num_refiner_layers, nh, nkv */
+int cmfc_nextdit_dims(const cmfc_nextdit* d, uint32_t dims[8]);
+
+/* NextDit::refine_caption (dit.rs:1201-1226): cap [cap_n, cap_feat] -> out [cap_n, hidden] */
+int cmfc_nextdit_refine_caption(cmfc_nextdit* d, const float* cap, size_t cap_n, float* out);
+/* NextDit::forward_with_cap (dit.rs:1389-1507): latent [c,h,w], refined caption, t -> pred [c,h,w] */
+int cmfc_nextdit_forward(cmfc_nextdit* d, const float* latent, size_t h, size_t w, const float* cap_e,
+                         size_t cap_n, float t, float* pred);
+/* NextDit::forward_cfg_pair (dit.rs:1238-1387) */
+int cmfc_nextdit_forward_pair(cmfc_nextdit* d, const float* latent, size_t h, size_t w, const float* cap_c,
+                              size_t cap_c_n, const float* cap_u, size_t cap_u_n, float t, float* pred_c,
+                              float* pred_u);
+/* Debug tap: copy the hidden state after joint block `layer` of the LAST forward call is not
+ * kept; instead this runs forward_pair and writes x after every joint block to
+ * taps [num_layers][n_c+n_u][hidden] (parity tests per block). */
+int cmfc_nextdit_forward_pair_taps(cmfc_nextdit* d, const float* latent, size_t h, size_t w, const float* cap_c,
+                                   size_t cap_c_n, const float* cap_u, size_t cap_u_n, float t, float* pred_c,
+                                   float* pred_u, float* taps);
+
+/* imagegen::denoise (imagegen.rs:143-217) for a BATCH of prompts on this device: every prompt's
+ * cond/uncond pair rides in one tall batch with one segment per sequence.
+ *   latents   [batch, c, h, w]  in: start noise, out: denoised latents
+ *   cap       [batch, cap_n, cap_feat]   raw caption features (refined once inside)
+ *   cap_u     [batch, cap_u_n, cap_feat] or NULL (no CFG)
+ * steps / guidance_scale as GenParams (imagegen.rs:41-55); sigma shift 6.0, CFG normalisation on. */
+int cmfc_denoise(cmfc_nextdit* d, float* latents, size_t batch, size_t h, size_t w, const float* cap, size_t cap_n,
+                 const float* cap_u, size_t cap_u_n, uint32_t steps, float guidance_scale);
+
+/* Split form of the loop for benchmarking one step with device-resident state:
+ * begin uploads inputs and refines captions; step runs denoise step i (0-based) of `steps`;
+ * end copies latents back.  cmfc_denoise == begin + steps x step + end. */
+int cmfc_denoise_begin(cmfc_nextdit* d, const float* latents, size_t batch, size_t h, size_t w, const float* cap,
+                       size_t cap_n, const float* cap_u, size_t cap_u_n, uint32_t steps, float guidance_scale);
+int cmfc_denoise_step(cmfc_nextdit* d, uint32_t i);
+int cmfc_denoise_end(cmfc_nextdit* d, float* latents);
+
+/* ---- quantizers on the device, byte-identical to the reference encoders
+ * (crates/cortiq-cli/src/convert.rs:551-566 encode_q8_row, :597-613 encode_q4_tiled,
+ * :883-992 encode_q4tp).  w [rows, cols] host f32 -> payload (host, caller-sized with
+ * cmfc_payload_nbytes, crates/cortiq-core/src/quant.rs:552-613 expected_nbytes). ---- */
+size_t cmfc_payload_nbytes(int dtype, size_t rows, size_t cols);
+int cmfc_encode(int dtype, const float* w, size_t rows, size_t cols, uint8_t* payload);
+/* same, generating w ~ N(0, std) on the device from `seed` (synthetic models for benchmarks) */
+int cmfc_encode_random(int dtype, uint64_t seed, float std, size_t rows, size_t cols, uint8_t* payload);
+
+/* ---- instrumentation ---- */
+/* kernels launched by this library on the current device since the last reset */
+uint64_t cmfc_launch_count(int reset);
+/* Time `iters` back-to-back launches of the dequant GEMM for tensor idx at M tokens with
+ * device-resident synthetic bf16 activations; mean milliseconds per launch (CUDA events on the
+ * library's stream).  mode: 0 f32 out, 1 bf16 out. */
+int cmfc_bench_gemm(cmfc_model* m, int64_t idx, size_t M, int mode, int iters, float* ms_per_launch);
+/* per-stage CUDA-event times of the last cmfc_denoise_step when profiling is on
+ * (categories of crates/cortiq-engine/src/dit.rs:192-217) */
+int cmfc_profile_enable(int on);
+int cmfc_profile_read(char* buf, size_t buflen);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CMF_CUDA_H */

@@ -1,0 +1,51 @@
+"""Build synthetic NextDiT containers for the tests: weights from tests/synth.py, quantized with
+the CPU oracle's encoders, written with the package's container writer."""
+import numpy as np
+
+from cmf_b200.container import CmfWriter
+from oracle import codecs as oc
+from oracle.nextdit import QWeight
+from tests import synth
+
+
+def build(cfg, path, plan, seed=0, norm_jitter=0.0, std=0.02):
+    """Returns (tensors_for_oracle, config_json).  ``plan`` maps tensor name -> dtype id; every
+    other tensor stays f32."""
+    t = synth.make_tensors(cfg, seed, norm_jitter, std)
+    w = CmfWriter(arch={"arch_name": "nextdit-synth", "hidden_size": cfg["hidden_size"],
+                        "num_layers": cfg["num_layers"], "vocab_size": 0})
+    oracle_t = {}
+    for name, arr in t.items():
+        dt = plan.get(name)
+        if dt is None or arr.ndim != 2:
+            w.add_f32(name, arr)
+            oracle_t[name] = arr
+        else:
+            q = QWeight.quantize(dt, arr)
+            w.add(name, dt, arr.shape, q.payload)
+            oracle_t[name] = q
+    cj = {k: cfg[k] for k in ("hidden_size", "num_layers", "num_refiner_layers", "num_attention_heads",
+                              "num_kv_heads", "in_channels", "patch_size", "axes_dim_rope", "norm_eps")}
+    w.add_json("dit.config_json", cj)
+    w.write(path)
+    return oracle_t, cj
+
+
+def single_weight_file(path, entries):
+    """entries: list of (name, dtype, f32 matrix).  Returns {name: QWeight}."""
+    w = CmfWriter(arch={"arch_name": "weights-only", "hidden_size": 0, "num_layers": 0, "vocab_size": 0})
+    out = {}
+    for name, dt, arr in entries:
+        q = QWeight.quantize(dt, arr)
+        w.add(name, dt, arr.shape, q.payload)
+        out[name] = q
+    # the reference's own one-tensor test files carry an f32 pad tensor as well
+    w.add_f32("pad", np.zeros((4, 4), np.float32))
+    w.write(path)
+    return out
+
+
+def rel_l2(a, b):
+    a = np.asarray(a, np.float64).ravel()
+    b = np.asarray(b, np.float64).ravel()
+    return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30))

@@ -1,0 +1,43 @@
+"""GPU parity of the flash attention kernel through the facade's dit_attention."""
+import numpy as np
+import pytest
+
+from oracle import codecs as oc
+from oracle.nextdit import attention_seq
+from tests.modelfile import rel_l2
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("nh,nkv,hd,n", [(4, 4, 64, 288), (6, 2, 96, 128), (6, 2, 96, 67), (24, 8, 96, 1100),
+                                          (2, 1, 128, 513), (2, 2, 32, 300)])
+def test_attention_matches_oracle(nh, nkv, hd, n):
+    from cmf_b200 import gpu
+    rng = np.random.default_rng(nh * 1000 + n)
+    q = oc.bf16_round(rng.standard_normal((n, nh, hd)).astype(np.float32))
+    k = oc.bf16_round(rng.standard_normal((n, nkv, hd)).astype(np.float32))
+    v = oc.bf16_round(rng.standard_normal((n, nkv, hd)).astype(np.float32))
+    out = np.empty((n, nh * hd), np.float32)
+    scale = 1.0 / np.sqrt(hd)
+    gpu.dit_attention(q.transpose(1, 0, 2), k.transpose(1, 0, 2), v.transpose(1, 0, 2), nh, nkv, n, hd, scale, out)
+    want = attention_seq(q.reshape(n, -1), k.reshape(n, -1), v.reshape(n, -1), nh, nkv, hd)
+    assert np.isfinite(out).all()
+    assert rel_l2(out, want) < 6e-3, rel_l2(out, want)
+
+
+def test_attention_sharp_and_flat_rows():
+    """Rows with one dominant key (max tracking) and rows with identical keys (uniform P)."""
+    from cmf_b200 import gpu
+    nh, nkv, hd, n = 2, 2, 64, 400
+    rng = np.random.default_rng(0)
+    q = rng.standard_normal((n, nh, hd)).astype(np.float32)
+    k = rng.standard_normal((n, nkv, hd)).astype(np.float32)
+    k[300] = q[5] * 4.0          # key 300 dominates query 5, found only in the third key tile
+    k[:, 1] = k[0:1, 1]          # head 1: all keys equal -> uniform attention
+    q, k = oc.bf16_round(q), oc.bf16_round(k)
+    v = oc.bf16_round(rng.standard_normal((n, nkv, hd)).astype(np.float32))
+    out = np.empty((n, nh * hd), np.float32)
+    gpu.dit_attention(q.transpose(1, 0, 2), k.transpose(1, 0, 2), v.transpose(1, 0, 2), nh, nkv, n, hd, 0.125, out)
+    want = attention_seq(q.reshape(n, -1), k.reshape(n, -1), v.reshape(n, -1), nh, nkv, hd)
+    assert rel_l2(out, want) < 6e-3
+    assert rel_l2(out.reshape(n, nh, hd)[:, 1], np.broadcast_to(v[:, 1].mean(0), (n, hd))) < 6e-3

@@ -1,0 +1,115 @@
+"""GPU parity of the dequant-fused GEMM through the facade entries q8_matmat / q4t_matmat /
+q4tp_matmat, dit_qkv and the fused FFN, against the strict CPU kernels of the oracle."""
+import numpy as np
+import pytest
+
+from oracle import codecs as oc
+from tests.modelfile import rel_l2, single_weight_file
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-2  # relative L2 on Y (north-star tolerance), inputs rounded to bf16 on the device
+
+
+def _call(gpu, dt, m, idx, x, rows, cols):
+    out = np.empty((x.shape[0], rows), np.float32)
+    if dt == oc.Q8_ROW:
+        gpu.q8_matmat(m, idx, None, x, x.shape[0], rows, cols, out)
+    elif dt == oc.Q4_TILED:
+        gpu.q4t_matmat(m, idx, x, x.shape[0], rows, cols, out)
+    else:
+        gpu.q4tp_matmat(m, idx, x, x.shape[0], rows, cols, out)
+    return out
+
+
+@pytest.mark.parametrize("dt", [oc.Q8_ROW, oc.Q4_TILED, oc.Q4TP])
+@pytest.mark.parametrize("shape", [(128, 64, 1), (128, 64, 256), (256, 256, 288), (384, 2304, 700), (2304, 1024, 33)])
+def test_matmat_small(tmp_path, dt, shape):
+    from cmf_b200 import Model, gpu
+    rows, cols, b = shape
+    rng = np.random.default_rng(rows + cols + b)
+    w = (rng.standard_normal((rows, cols)) * 0.02).astype(np.float32)
+    x = oc.bf16_round(rng.standard_normal((b, cols)).astype(np.float32))
+    path = str(tmp_path / "w.cmf")
+    q = single_weight_file(path, [("w", dt, w)])["w"]
+    with Model(path) as m:
+        got = _call(gpu, dt, m, m.index("w"), x, rows, cols)
+        # twice: the second call runs against resident weights and reused workspaces
+        got2 = _call(gpu, dt, m, m.index("w"), x, rows, cols)
+    want = oc.matmat_exact(dt, q.payload, rows, cols, x)
+    assert np.array_equal(got, got2)
+    err = rel_l2(got, want)
+    # q8 levels are exact in bf16 and x is bf16-exact: only f32 summation order differs
+    assert err < (2e-5 if dt == oc.Q8_ROW else 4e-3), err
+    assert err < TOL
+
+
+@pytest.mark.parametrize("dt", [oc.Q8_ROW, oc.Q4_TILED, oc.Q4TP])
+def test_matmat_sweep_shapes_sampled(tmp_path, dt):
+    """The op-sweep shapes at M = 4352; the strict CPU kernel checks 24 sampled rows of X."""
+    from cmf_b200 import Model, gpu
+    rng = np.random.default_rng(1)
+    for K, N in ((2304, 2304), (2304, 6912), (9216, 2304)):
+        M = 4352
+        w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+        x = oc.bf16_round(rng.standard_normal((M, K)).astype(np.float32))
+        path = str(tmp_path / f"w{K}_{N}.cmf")
+        q = single_weight_file(path, [("w", dt, w)])["w"]
+        with Model(path) as m:
+            got = _call(gpu, dt, m, m.index("w"), x, N, K)
+        pick = np.sort(rng.choice(M, 24, replace=False))
+        pick[0], pick[-1] = 0, M - 1
+        want = oc.matmat_exact(dt, q.payload, N, K, x[pick])
+        err = rel_l2(got[pick], want)
+        assert err < TOL, (K, N, err)
+        assert np.isfinite(got).all()
+        # linearity over the full output: Y(2x) == 2 Y(x) exactly (power-of-two scaling)
+    
+
+def test_matmat_rejects_wrong_codec_and_shape(tmp_path):
+    from cmf_b200 import CmfCudaError, Model, gpu
+    rng = np.random.default_rng(0)
+    w = (rng.standard_normal((128, 64)) * 0.02).astype(np.float32)
+    path = str(tmp_path / "w.cmf")
+    single_weight_file(path, [("w", oc.Q8_ROW, w), ("odd", oc.Q8_ROW, w[:100])])
+    x = np.zeros((4, 64), np.float32)
+    out = np.empty((4, 128), np.float32)
+    with Model(path) as m:
+        with pytest.raises(CmfCudaError) as e:
+            gpu.q4t_matmat(m, m.index("w"), x, 4, 128, 64, out)
+        assert e.value.code == -2
+        with pytest.raises(CmfCudaError) as e:
+            gpu.q8_matmat(m, m.index("w"), None, x, 4, 64, 128, np.empty((4, 64), np.float32))
+        assert e.value.code == -3
+        with pytest.raises(CmfCudaError) as e:  # 100 rows: not a multiple of the 128-row tile
+            gpu.q8_matmat(m, m.index("odd"), None, x, 4, 100, 64, np.empty((4, 100), np.float32))
+        assert e.value.code == -3
+        with pytest.raises(CmfCudaError):
+            gpu.q8_matmat(m, 99, None, x, 4, 128, 64, out)
+
+
+@pytest.mark.parametrize("codecs", [(oc.Q8_ROW, oc.Q8_ROW), (oc.Q4TP, oc.Q4_TILED), (oc.Q4_TILED, oc.Q4TP)])
+def test_qkv_and_ffn(tmp_path, codecs):
+    from cmf_b200 import Model, gpu
+    from oracle.nextdit import silu
+    hs, inter, nq, nkv, b = 256, 1024, 256, 128, 300
+    rng = np.random.default_rng(4)
+    mats = {"q": (nq, hs), "k": (nkv, hs), "v": (nkv, hs), "w1": (inter, hs), "w3": (inter, hs), "w2": (hs, inter)}
+    ws = {k: (rng.standard_normal(s) * 0.05).astype(np.float32) for k, s in mats.items()}
+    a, f = codecs
+    entries = [(k, a if k in "qkv" else f, v) for k, v in ws.items()]
+    path = str(tmp_path / "w.cmf")
+    qs = single_weight_file(path, entries)
+    x = oc.bf16_round(rng.standard_normal((b, hs)).astype(np.float32))
+    with Model(path) as m:
+        qo, ko, vo = (np.empty((b, nq), np.float32), np.empty((b, nkv), np.float32), np.empty((b, nkv), np.float32))
+        gpu.dit_qkv(m, m.index("q"), m.index("k"), m.index("v"), x, b, hs, nq, nkv, qo, ko, vo)
+        out = np.empty((b, hs), np.float32)
+        gpu.q4t_ffn(m, m.index("w1"), m.index("w3"), m.index("w2"), x, b, hs, inter, out)
+    for got, k in ((qo, "q"), (ko, "k"), (vo, "v")):
+        want = oc.matmat_exact(qs[k].dtype, qs[k].payload, *mats[k], x)
+        assert rel_l2(got, want) < 4e-3, k
+    g = oc.matmat_exact(qs["w1"].dtype, qs["w1"].payload, inter, hs, x)
+    u = oc.matmat_exact(qs["w3"].dtype, qs["w3"].payload, inter, hs, x)
+    want = oc.matmat_exact(qs["w2"].dtype, qs["w2"].payload, hs, inter, silu(g) * u)
+    assert rel_l2(out, want) < TOL
