@@ -28,6 +28,7 @@ SYMBOLS = {
     "cmfc_model_find": (C.c_int64, [C.c_void_p, C.c_char_p]),
     "cmfc_model_tensor_info": (C.c_int, [C.c_void_p, C.c_int64, C.POINTER(C.c_int), C.POINTER(C.c_int),
                                          C.POINTER(C.c_uint32), C.POINTER(C.c_uint64)]),
+    "cmfc_model_tensor_name": (C.c_char_p, [C.c_void_p, C.c_int64]),
     "cmfc_model_tensor_bytes": (C.c_void_p, [C.c_void_p, C.c_int64]),
     "cmfc_weight_is_resident": (C.c_int, [C.c_void_p, C.c_int64]),
     "cmfc_weight_dequant": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_size_t]),
@@ -66,6 +67,9 @@ SYMBOLS = {
     "cmfc_encode_random": (C.c_int, [C.c_int, C.c_uint64, C.c_float, C.c_size_t, C.c_size_t, C.c_void_p]),
     "cmfc_launch_count": (C.c_uint64, [C.c_int]),
     "cmfc_bench_gemm": (C.c_int, [C.c_void_p, C.c_int64, C.c_size_t, C.c_int, C.c_int, C.POINTER(C.c_float)]),
+    "cmfc_bench_attention": (C.c_int, [C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t, C.c_int, C.POINTER(C.c_float)]),
+    "cmfc_bench_rowop": (C.c_int, [C.c_int, C.c_size_t, C.c_size_t, C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_double)]),
+    "cmfc_stream_handle": (C.c_void_p, []),
     "cmfc_profile_enable": (C.c_int, [C.c_int]),
     "cmfc_profile_read": (C.c_int, [C.c_char_p, C.c_size_t]),
 }

@@ -135,6 +135,10 @@ class Model:
     def index(self, name):
         return int(check(lib().cmfc_model_find(self.handle, name.encode())))
 
+    def name(self, idx):
+        n = lib().cmfc_model_tensor_name(self.handle, idx)
+        return n.decode() if n else None
+
     def info(self, idx):
         dt, nd, nb = C.c_int(), C.c_int(), C.c_uint64()
         shape = (C.c_uint32 * 6)()

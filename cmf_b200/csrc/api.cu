@@ -68,6 +68,10 @@ extern "C" int cmfc_model_tensor_info(const cmfc_model* m, int64_t idx, int* dty
     if (nbytes) *nbytes = t.nbytes;
     return OK;
 }
+extern "C" const char* cmfc_model_tensor_name(const cmfc_model* m, int64_t idx) {
+    if (!m || idx < 0 || idx >= (int64_t)m->m->recs.size()) return nullptr;
+    return m->m->recs[idx].name.c_str();
+}
 extern "C" const void* cmfc_model_tensor_bytes(const cmfc_model* m, int64_t idx) {
     if (!m || idx < 0 || idx >= (int64_t)m->m->recs.size()) return nullptr;
     return m->m->bytes(idx);
@@ -929,6 +933,104 @@ extern "C" int cmfc_bench_gemm(cmfc_model* m, int64_t idx, size_t M, int mode, i
     cudaEventDestroy(e1);
     *ms_per_launch = ms / iters;
     return check_status(c, "bench_gemm");
+}
+
+extern "C" int cmfc_bench_attention(size_t nh, size_t nkv, size_t hd, size_t n, size_t nseg, int iters, float* ms_per_launch) {
+    NEED(ms_per_launch && nh && nkv && n && nseg && iters > 0, "bench_attention: bad argument");
+    NEED_CTX();
+    std::vector<int> segs(nseg, (int)n);
+    SegTable st;
+    CMFC_TRY(prepare_segs(c, segs, &st));
+    const size_t tot = n * nseg, qn = tot * nh * hd, kn = tot * nkv * hd, vn = (size_t)nkv * hd * st.vt_pitch;
+    DevBuf &f = c->buf("ba_f"), &q = c->buf("ba_q"), &k = c->buf("ba_k"), &v = c->buf("ba_v"), &o = c->buf("ba_o");
+    CMFC_TRY(f.ensure((qn > vn ? qn : vn) * 4));
+    CMFC_TRY(q.ensure(qn * 2));
+    CMFC_TRY(k.ensure(kn * 2));
+    CMFC_TRY(v.ensure(vn * 2));
+    CMFC_TRY(o.ensure(qn * 2));
+    launch_fill_normal(f.as<float>(), qn, 11, 1.0f, c->stream);
+    launch_f32_to_bf16(f.as<float>(), q.as<__nv_bfloat16>(), qn, c->stream);
+    launch_fill_normal(f.as<float>(), kn, 12, 1.0f, c->stream);
+    launch_f32_to_bf16(f.as<float>(), k.as<__nv_bfloat16>(), kn, c->stream);
+    launch_fill_normal(f.as<float>(), vn, 13, 1.0f, c->stream);
+    launch_f32_to_bf16(f.as<float>(), v.as<__nv_bfloat16>(), vn, c->stream);
+    c->launches += 6;
+    const float scale = 1.0f / sqrtf((float)hd);
+    for (int i = 0; i < 3; ++i)
+        CMFC_TRY(dev_attention(c, q.as<__nv_bfloat16>(), k.as<__nv_bfloat16>(), v.as<__nv_bfloat16>(), st, (int)nh, (int)nkv, (int)hd, scale, o.as<__nv_bfloat16>()));
+    cudaEvent_t e0, e1;
+    CMFC_CUDA(cudaEventCreate(&e0));
+    CMFC_CUDA(cudaEventCreate(&e1));
+    CMFC_CUDA(cudaEventRecord(e0, c->stream));
+    for (int i = 0; i < iters; ++i)
+        CMFC_TRY(dev_attention(c, q.as<__nv_bfloat16>(), k.as<__nv_bfloat16>(), v.as<__nv_bfloat16>(), st, (int)nh, (int)nkv, (int)hd, scale, o.as<__nv_bfloat16>()));
+    CMFC_CUDA(cudaEventRecord(e1, c->stream));
+    CMFC_CUDA(cudaEventSynchronize(e1));
+    float ms = 0;
+    CMFC_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    *ms_per_launch = ms / iters;
+    return check_status(c, "bench_attention");
+}
+
+// kind: 0 modulated RMSNorm (f32 -> bf16), 1 gated residual, 2 gated residual fused with the next
+// modulated norm, 3 qk-norm + RoPE + head packing (cols = hidden; nh/nkv/hd as Lumina-2 when hidden = 2304)
+extern "C" int cmfc_bench_rowop(int kind, size_t rows, size_t cols, int iters, float* ms_per_launch, double* bytes_per_launch) {
+    NEED(ms_per_launch && bytes_per_launch && rows && cols && iters > 0 && kind >= 0 && kind <= 3, "bench_rowop: bad argument");
+    NEED_CTX();
+    if (!row_cols_supported((int)cols)) return fail(ERR_UNSUPPORTED, "bench_rowop: unsupported row width");
+    DevBuf &x = c->buf("br_x"), &src = c->buf("br_src"), &vec = c->buf("br_vec"), &ob = c->buf("br_ob"), &tab = c->buf("br_tab"), &o2 = c->buf("br_o2"), &o3 = c->buf("br_o3");
+    const int hd = cols % 96 == 0 ? 96 : 64, nh = (int)cols / hd, nkv = nh % 3 == 0 ? nh / 3 : nh;
+    const size_t qkvw = (size_t)(nh + 2 * nkv) * hd;
+    CMFC_TRY(x.ensure(rows * (kind == 3 ? qkvw : cols) * 4));
+    CMFC_TRY(src.ensure(rows * cols * 4));
+    CMFC_TRY(vec.ensure(4 * cols * 4));
+    CMFC_TRY(ob.ensure(rows * cols * 2));
+    launch_fill_normal(x.as<float>(), rows * (kind == 3 ? qkvw : cols), 21, 1.0f, c->stream);
+    launch_fill_normal(src.as<float>(), rows * cols, 22, 1.0f, c->stream);
+    launch_fill_normal(vec.as<float>(), 4 * cols, 23, 0.1f, c->stream);
+    const float* v0 = vec.as<float>();
+    std::vector<int> segs(1, (int)rows);
+    SegTable st;
+    if (kind == 3) {
+        CMFC_TRY(prepare_segs(c, segs, &st));
+        CMFC_TRY(tab.ensure(rows * hd * 8));
+        CMFC_TRY(o2.ensure(rows * nkv * hd * 2));
+        CMFC_TRY(o3.ensure((size_t)nkv * hd * st.vt_pitch * 2));
+        CMFC_CUDA(cudaMemsetAsync(tab.p, 0, rows * hd * 8, c->stream));
+    }
+    auto run = [&]() {
+        if (kind == 0) launch_rms_mod(x.as<float>(), v0, v0 + cols, 1e-5, (int)rows, (int)cols, ob.as<__nv_bfloat16>(), nullptr, c->stream);
+        else if (kind == 1) launch_gated_residual(x.as<float>(), src.as<float>(), v0, v0 + cols, 1e-5, (int)rows, (int)cols, c->stream);
+        else if (kind == 2) launch_residual_then_norm(x.as<float>(), src.as<float>(), v0, v0 + cols, v0 + 2 * cols, v0 + 3 * cols, 1e-5, (int)rows, (int)cols, ob.as<__nv_bfloat16>(), c->stream);
+        else launch_qk_rope_pack(x.as<float>(), (int)rows, nh, nkv, hd, v0, v0 + hd, tab.as<double>(), tab.as<double>() + rows * hd / 2, ob.as<__nv_bfloat16>(), o2.as<__nv_bfloat16>(), o3.as<__nv_bfloat16>(), st.vt_pitch, st.dev, 1, st.max_seg, c->stream);
+        c->launches += kind == 3 ? 2 : 1;
+    };
+    for (int i = 0; i < 3; ++i) run();
+    cudaEvent_t e0, e1;
+    CMFC_CUDA(cudaEventCreate(&e0));
+    CMFC_CUDA(cudaEventCreate(&e1));
+    CMFC_CUDA(cudaEventRecord(e0, c->stream));
+    for (int i = 0; i < iters; ++i) run();
+    CMFC_CUDA(cudaEventRecord(e1, c->stream));
+    CMFC_CUDA(cudaEventSynchronize(e1));
+    float ms = 0;
+    CMFC_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    *ms_per_launch = ms / iters;
+    const double e = (double)rows * cols;
+    // algorithmic bytes: f32 reads/writes 4 B, bf16 writes 2 B per element
+    *bytes_per_launch = kind == 0 ? e * 6 : kind == 1 ? e * 12 : kind == 2 ? e * 14
+                                  : (double)rows * (qkvw * 4 + qkvw * 2 + (double)(hd / 2) * 16);
+    CMFC_CUDA(cudaGetLastError());
+    return OK;
+}
+
+extern "C" void* cmfc_stream_handle(void) {
+    Context* c = ctx();
+    return c ? (void*)c->stream : nullptr;
 }
 
 extern "C" int cmfc_profile_enable(int on) {

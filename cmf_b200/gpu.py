@@ -209,6 +209,19 @@ def bench_gemm(model: Model, idx, M, mode=0, iters=10):
     return ms.value
 
 
+def bench_attention(nh, nkv, hd, n, nseg=1, iters=5):
+    ms = C.c_float()
+    check(lib().cmfc_bench_attention(nh, nkv, hd, n, nseg, iters, C.byref(ms)))
+    return ms.value
+
+
+def bench_rowop(kind, rows, cols, iters=10):
+    """-> (ms per launch, algorithmic bytes per launch)"""
+    ms, nb = C.c_float(), C.c_double()
+    check(lib().cmfc_bench_rowop(kind, rows, cols, iters, C.byref(ms), C.byref(nb)))
+    return ms.value, nb.value
+
+
 def profile_enable(on=True):
     check(lib().cmfc_profile_enable(int(on)))
 
@@ -218,3 +231,8 @@ def profile_read():
     buf = C.create_string_buffer(8192)
     check(lib().cmfc_profile_read(buf, len(buf)))
     return json.loads(buf.value.decode())
+
+
+def stream_handle():
+    """Raw cudaStream_t of the current device context (for external event timing)."""
+    return int(lib().cmfc_stream_handle() or 0)

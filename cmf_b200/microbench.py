@@ -1,0 +1,78 @@
+"""Kernel micro-benchmarks on synthetic device-resident inputs (CUDA-event timing inside the
+library).  Used for the per-kernel roofline tables and as the small cases for profiler captures.
+
+    python -m cmf_b200.microbench gemm --codec q4t --N 2304 --K 2304 --M 8704
+    python -m cmf_b200.microbench attention --n 4352 --nseg 2
+    python -m cmf_b200.microbench rowops --rows 8704
+    python -m cmf_b200.microbench sweep          # the op-level dequant-GEMM sweep of the baseline config
+"""
+import argparse
+import json
+import os
+import tempfile
+
+from . import gpu
+from .container import CmfWriter, Model
+from .synth import CODECS
+
+ROWOPS = {0: "rms_mod", 1: "gated_residual", 2: "residual_then_norm", 3: "qk_rope_pack"}
+
+
+def _weight_file(entries):
+    path = os.path.join(tempfile.gettempdir(), f"cmf_microbench_{os.getpid()}.cmf")
+    w = CmfWriter(arch={"arch_name": "microbench"})
+    for name, dt, N, K, seed in entries:
+        w.add(name, dt, (N, K), gpu.encode_random(dt, seed, 0.02, N, K))
+    w.write(path, hash_tensors=False)
+    return path
+
+
+def gemm(codec, N, K, M, iters, mode=0):
+    path = _weight_file([("w", CODECS[codec], N, K, 7)])
+    try:
+        with Model(path) as m:
+            ms = gpu.bench_gemm(m, m.index("w"), M, mode=mode, iters=iters)
+    finally:
+        os.remove(path)
+    bpw = {"q8": 1.0, "q4t": 0.5625, "q4tp": 0.5195}[codec]
+    return {"kernel": "gemm_dequant", "codec": codec, "M": M, "N": N, "K": K, "ms": ms,
+            "tflops": 2.0 * M * N * K / (ms * 1e-3) / 1e12,
+            "algorithmic_bytes": K * N * bpw + 2.0 * M * K + (4.0 if mode == 0 else 2.0) * M * N}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["gemm", "attention", "rowops", "sweep"])
+    ap.add_argument("--codec", default="q4t", choices=["q8", "q4t", "q4tp"])
+    ap.add_argument("--N", type=int, default=2304)
+    ap.add_argument("--K", type=int, default=2304)
+    ap.add_argument("--M", type=int, default=8704)
+    ap.add_argument("--n", type=int, default=4352)
+    ap.add_argument("--nseg", type=int, default=2)
+    ap.add_argument("--rows", type=int, default=8704)
+    ap.add_argument("--cols", type=int, default=2304)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--device", type=int, default=0)
+    a = ap.parse_args()
+    gpu.set_current_device(a.device)
+    if a.what == "gemm":
+        print(json.dumps(gemm(a.codec, a.N, a.K, a.M, a.iters)))
+    elif a.what == "attention":
+        ms = gpu.bench_attention(24, 8, 96, a.n, a.nseg, a.iters)
+        fl = 4.0 * a.n * a.n * 24 * 96 * a.nseg
+        print(json.dumps({"kernel": "attention", "nh": 24, "nkv": 8, "hd": 96, "n": a.n, "nseg": a.nseg, "ms": ms,
+                          "tflops": fl / (ms * 1e-3) / 1e12}))
+    elif a.what == "rowops":
+        for kind, name in ROWOPS.items():
+            ms, nb = gpu.bench_rowop(kind, a.rows, a.cols, a.iters)
+            print(json.dumps({"kernel": name, "rows": a.rows, "cols": a.cols, "ms": ms, "algorithmic_bytes": nb,
+                              "gbs": nb / (ms * 1e-3) / 1e9}))
+    else:
+        for codec in ("q8", "q4t", "q4tp"):
+            for K, N in ((2304, 2304), (2304, 6912), (2304, 9216), (9216, 2304)):
+                for M in (256, 4352, 17408):
+                    print(json.dumps(gemm(codec, N, K, M, a.iters)), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,82 @@
+"""Synthetic NextDiT containers for benchmarks and demos: random-init weights N(0, std) are
+generated AND quantized on the device (byte-identical to the reference encoders), then written
+as a regular .cmf file that the library memory-maps like any packed model."""
+import os
+
+import numpy as np
+
+from . import gpu
+from .container import CmfWriter, DT_F32, DT_Q4TP, DT_Q4_TILED, DT_Q8_ROW
+
+# Lumina-Image-2.0 geometry (2.6 B parameters)
+LUMINA2 = dict(hidden_size=2304, num_layers=26, num_refiner_layers=2, num_attention_heads=24, num_kv_heads=8,
+               in_channels=16, patch_size=2, axes_dim_rope=[32, 32, 32], norm_eps=1e-5, inter=9216, cap_feat=2304)
+TINY = dict(hidden_size=256, num_layers=2, num_refiner_layers=2, num_attention_heads=4, num_kv_heads=4,
+            in_channels=16, patch_size=2, axes_dim_rope=[32, 16, 16], norm_eps=1e-5, inter=1024, cap_feat=256)
+
+CODECS = {"q8": DT_Q8_ROW, "q4t": DT_Q4_TILED, "q4tp": DT_Q4TP, "f32": DT_F32}
+
+
+def tensor_list(cfg, attn, ffn):
+    """[(name, dtype id, shape, kind)] in the order the reference's packer would emit
+    (crates/cortiq-cli/src/imagepack.rs:156-178): modulation linears q8_row, attention / FFN /
+    caption projections at the chosen level, everything else f32.  kind: 'w' weight ~N(0,std),
+    'b' bias ~N(0,std), 'n' norm weight (ones)."""
+    hs, nh, nkv = cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_kv_heads"]
+    hd = hs // nh
+    inter, cap_feat = cfg["inter"], cfg["cap_feat"]
+    pv = cfg["patch_size"] ** 2 * cfg["in_channels"]
+    temb = min(hs, 1024)
+    out = [("dit.x_embedder.weight", DT_F32, (hs, pv), "w"), ("dit.x_embedder.bias", DT_F32, (hs,), "b")]
+    p = "dit.time_caption_embed."
+    out += [(p + "timestep_embedder.linear_1.weight", DT_F32, (temb, 256), "w"),
+            (p + "timestep_embedder.linear_1.bias", DT_F32, (temb,), "b"),
+            (p + "timestep_embedder.linear_2.weight", DT_F32, (temb, temb), "w"),
+            (p + "timestep_embedder.linear_2.bias", DT_F32, (temb,), "b"),
+            (p + "caption_embedder.0.weight", DT_F32, (cap_feat,), "n"),
+            (p + "caption_embedder.1.weight", attn, (hs, cap_feat), "w"),
+            (p + "caption_embedder.1.bias", DT_F32, (hs,), "b")]
+    for group, count, modulated in (("context_refiner", cfg["num_refiner_layers"], False),
+                                    ("noise_refiner", cfg["num_refiner_layers"], True),
+                                    ("layers", cfg["num_layers"], True)):
+        for l in range(count):
+            b = f"dit.{group}.{l}"
+            if modulated:
+                out += [(b + ".norm1.linear.weight", DT_Q8_ROW, (4 * hs, temb), "w"),
+                        (b + ".norm1.linear.bias", DT_F32, (4 * hs,), "b"),
+                        (b + ".norm1.norm.weight", DT_F32, (hs,), "n")]
+            else:
+                out += [(b + ".norm1.weight", DT_F32, (hs,), "n")]
+            out += [(b + ".attn.to_q.weight", attn, (nh * hd, hs), "w"), (b + ".attn.to_k.weight", attn, (nkv * hd, hs), "w"),
+                    (b + ".attn.to_v.weight", attn, (nkv * hd, hs), "w"), (b + ".attn.to_out.0.weight", attn, (hs, nh * hd), "w"),
+                    (b + ".attn.norm_q.weight", DT_F32, (hd,), "n"), (b + ".attn.norm_k.weight", DT_F32, (hd,), "n"),
+                    (b + ".norm2.weight", DT_F32, (hs,), "n"), (b + ".ffn_norm1.weight", DT_F32, (hs,), "n"),
+                    (b + ".feed_forward.linear_1.weight", ffn, (inter, hs), "w"),
+                    (b + ".feed_forward.linear_3.weight", ffn, (inter, hs), "w"),
+                    (b + ".feed_forward.linear_2.weight", ffn, (hs, inter), "w"),
+                    (b + ".ffn_norm2.weight", DT_F32, (hs,), "n")]
+    out += [("dit.norm_out.linear_1.weight", DT_F32, (hs, temb), "w"), ("dit.norm_out.linear_1.bias", DT_F32, (hs,), "b"),
+            ("dit.norm_out.linear_2.weight", DT_F32, (pv, hs), "w"), ("dit.norm_out.linear_2.bias", DT_F32, (pv,), "b")]
+    return out
+
+
+def write_model(path, cfg, attn="q8", ffn="q8", seed=0, std=0.02):
+    """Write a synthetic model; every tensor's values are a pure function of (seed, position in
+    the list), so two ranks writing the same arguments produce identical files."""
+    attn, ffn = CODECS[attn], CODECS[ffn]
+    w = CmfWriter(arch={"arch_name": "nextdit-synth", "hidden_size": cfg["hidden_size"],
+                        "num_layers": cfg["num_layers"], "vocab_size": 0}, quant_type="mixed")
+    for i, (name, dt, shape, kind) in enumerate(tensor_list(cfg, attn, ffn)):
+        if kind == "n":
+            w.add_f32(name, np.ones(shape, np.float32))
+            continue
+        rows, cols = (shape[0], shape[1]) if len(shape) == 2 else (1, shape[0])
+        payload = gpu.encode_random(dt, seed * 100003 + i + 1, std, rows, cols)
+        w.add(name, dt, shape, payload)
+    cj = {k: cfg[k] for k in ("hidden_size", "num_layers", "num_refiner_layers", "num_attention_heads",
+                              "num_kv_heads", "in_channels", "patch_size", "axes_dim_rope", "norm_eps")}
+    w.add_json("dit.config_json", cj)
+    tmp = path + f".tmp{os.getpid()}"
+    w.write(tmp, hash_tensors=False)
+    os.replace(tmp, path)
+    return path

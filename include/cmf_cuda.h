@@ -65,6 +65,8 @@ int64_t cmfc_model_find(const cmfc_model* m, const char* name);
 /* directory record idx -> dtype id, ndim, shape[6], payload bytes */
 int cmfc_model_tensor_info(const cmfc_model* m, int64_t idx, int* dtype, int* ndim, uint32_t shape[6],
                            uint64_t* nbytes);
+/* name of directory record idx (valid until close), NULL when out of range */
+const char* cmfc_model_tensor_name(const cmfc_model* m, int64_t idx);
 /* pointer into the mapping (valid until close) */
 const void* cmfc_model_tensor_bytes(const cmfc_model* m, int64_t idx);
 
@@ -180,6 +182,15 @@ uint64_t cmfc_launch_count(int reset);
  * device-resident synthetic bf16 activations; mean milliseconds per launch (CUDA events on the
  * library's stream).  mode: 0 f32 out, 1 bf16 out. */
 int cmfc_bench_gemm(cmfc_model* m, int64_t idx, size_t M, int mode, int iters, float* ms_per_launch);
+/* Time the flash-attention kernel on synthetic bf16 inputs: nseg segments of n tokens each. */
+int cmfc_bench_attention(size_t nh, size_t nkv, size_t hd, size_t n, size_t nseg, int iters, float* ms_per_launch);
+/* Time a bandwidth-bound row kernel on synthetic inputs; also returns its algorithmic bytes per
+ * launch.  kind: 0 modulated RMSNorm, 1 gated residual, 2 gated residual + next modulated norm
+ * (one pass), 3 qk-norm + RoPE + head packing. */
+int cmfc_bench_rowop(int kind, size_t rows, size_t cols, int iters, float* ms_per_launch, double* bytes_per_launch);
+/* the cudaStream_t every kernel of the current device's context is launched on (so a caller can
+ * record its own events around library work) */
+void* cmfc_stream_handle(void);
 /* per-stage CUDA-event times of the last cmfc_denoise_step when profiling is on
  * (categories of crates/cortiq-engine/src/dit.rs:192-217) */
 int cmfc_profile_enable(int on);

@@ -22,8 +22,9 @@ from . import codecs
 class QWeight:
     """A quantized projection as stored in the container: dtype id, shape, payload bytes."""
 
-    def __init__(self, dtype, rows, cols, payload):
+    def __init__(self, dtype, rows, cols, payload, cache=True):
         self.dtype, self.rows, self.cols = dtype, rows, cols
+        self.cache = cache
         self.payload = np.ascontiguousarray(np.frombuffer(bytes(payload), np.uint8)) \
             if not isinstance(payload, np.ndarray) else payload
         self._dense = None
@@ -34,9 +35,12 @@ class QWeight:
         return cls(dtype, w.shape[0], w.shape[1], codecs.encode(dtype, w))
 
     def dense(self):
-        if self._dense is None:
-            self._dense = codecs.dequant(self.dtype, self.payload, self.rows, self.cols)
-        return self._dense
+        if self._dense is not None:
+            return self._dense
+        d = codecs.dequant(self.dtype, self.payload, self.rows, self.cols)
+        if self.cache:
+            self._dense = d
+        return d
 
 
 def matmat(w, x, exact=False):

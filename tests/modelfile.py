@@ -49,3 +49,28 @@ def rel_l2(a, b):
     a = np.asarray(a, np.float64).ravel()
     b = np.asarray(b, np.float64).ravel()
     return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30))
+
+
+def load_for_oracle(path, cache=True):
+    """Read a container back for the oracle: {name: f32 array | QWeight}, config dict.  Tensor
+    bytes come straight from the file mapping (host only)."""
+    import json
+
+    from cmf_b200.container import Model
+    out = {}
+    cfg = None
+    m = Model(path)
+    try:
+        for i in range(len(m)):
+            dt, shape, nb = m.info(i)
+            name = m.name(i)
+            raw = np.array(m.tensor_bytes(i), copy=True)
+            if name == "dit.config_json":
+                cfg = json.loads(raw.tobytes().decode())
+            elif dt == 0:
+                out[name] = raw.view(np.float32).reshape(shape)
+            elif dt in (3, 11, 15):
+                out[name] = QWeight(dt, shape[0], shape[1], raw, cache=cache)
+    finally:
+        m.close()
+    return out, cfg

@@ -127,7 +127,6 @@ def test_q4tp_ladder_is_iterated():  # quant.rs:396-411: one exp2 then 31 multip
     for c in range(32):
         assert abs(t[c] - x) <= 2e-7 * x  # libm exp2f vs numpy exp2 may differ in the last bit
         x = np.float32(x * r)
-    assert all(t[c] == np.float32(t[c - 1] * np.float32(t[1] / t[0])) or True for c in range(1, 32))
 
 
 def test_exact_matmat_equals_dense_product():  # qtensor.rs:10702: exact path == dequant then dot
@@ -280,4 +279,4 @@ def test_bad_arguments_never_reach_a_launch():
     assert L.cmfc_payload_nbytes(3, 4, 8) == 4 * 8 + 8
     assert L.cmfc_payload_nbytes(11, 4, 64) == 4 * 2 * 18
     assert L.cmfc_payload_nbytes(15, 7, 64) == 7 * 2 * 16 + 7 * 4 + 7 * 2
-    assert b"null" in L.cmfc_last_error() or True
+    assert b"null" in L.cmfc_last_error()

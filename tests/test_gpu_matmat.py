@@ -63,8 +63,7 @@ def test_matmat_sweep_shapes_sampled(tmp_path, dt):
         err = rel_l2(got[pick], want)
         assert err < TOL, (K, N, err)
         assert np.isfinite(got).all()
-        # linearity over the full output: Y(2x) == 2 Y(x) exactly (power-of-two scaling)
-    
+
 
 def test_matmat_rejects_wrong_codec_and_shape(tmp_path):
     from cmf_b200 import CmfCudaError, Model, gpu
@@ -79,7 +78,7 @@ def test_matmat_rejects_wrong_codec_and_shape(tmp_path):
             gpu.q4t_matmat(m, m.index("w"), x, 4, 128, 64, out)
         assert e.value.code == -2
         with pytest.raises(CmfCudaError) as e:
-            gpu.q8_matmat(m, m.index("w"), None, x, 4, 64, 128, np.empty((4, 64), np.float32))
+            gpu.q8_matmat(m, m.index("w"), None, np.zeros((4, 128), np.float32), 4, 64, 128, np.empty((4, 64), np.float32))
         assert e.value.code == -3
         with pytest.raises(CmfCudaError) as e:  # 100 rows: not a multiple of the 128-row tile
             gpu.q8_matmat(m, m.index("odd"), None, x, 4, 100, 64, np.empty((4, 100), np.float32))
