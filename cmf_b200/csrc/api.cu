@@ -472,6 +472,8 @@ void rope_rows(const std::vector<int>& ids3, const int axes[3], std::vector<doub
 int upload_rope(Context* c, DevBuf* buf, const std::vector<int>& ids3, const int axes[3]) {
     std::vector<double> cs, sn;
     rope_rows(ids3, axes, &cs, &sn);
+    // kernels already queued on the stream may still read the previous table
+    CMFC_CUDA(cudaStreamSynchronize(c->stream));
     CMFC_TRY(buf->ensure(cs.size() * 16));
     CMFC_CUDA(cudaMemcpy(buf->p, cs.data(), cs.size() * 8, cudaMemcpyHostToDevice));
     CMFC_CUDA(cudaMemcpy(buf->as<double>() + cs.size(), sn.data(), sn.size() * 8, cudaMemcpyHostToDevice));

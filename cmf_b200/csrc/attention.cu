@@ -10,9 +10,11 @@
 //   softmax        four warps per query tile, one query row per thread: tcgen05.ld the row,
 //                  running max / sum in the exp2 domain, P packed to bf16 and written back
 //                  over the S columns with tcgen05.st
-//   R = P V        tcgen05.mma with P as the TMEM A operand and V^T (keys contiguous, 128-byte
-//                  swizzle) from shared memory, into a per-tile TMEM scratch
-//   O = O*alpha+R  in registers (f32), so rescaling never touches TMEM
+//   O += P V       tcgen05.mma with P as the TMEM A operand and V^T (keys contiguous, 128-byte
+//                  swizzle) from shared memory, accumulating into the tile's O columns in TMEM
+//   rescale        lazily: the reference maximum of a row moves only when the new maximum exceeds
+//                  it by more than 8 (in log2 units), so P stays below 2^8 and the O row in TMEM
+//                  is multiplied by exp2(m_old - m_new) on the few tiles where that happens
 // While the softmax warps of tile A work, the tensor core runs tile B, and vice versa.
 #include "common.cuh"
 #include "kernels.h"
@@ -24,7 +26,7 @@ constexpr int QT = 128;   // query rows per tile (UMMA M)
 constexpr int KT = 128;   // keys per tile (UMMA N for S, K extent for P V)
 constexpr int KV_STAGES = 2;
 constexpr int ATTN_THREADS = 32 * 10;  // TMA, MMA, 4 softmax warps for tile A, 4 for tile B
-// TMEM columns: S (and P over it) of tile A / B at 0 / 128, the P V scratch at 256 / 384
+// TMEM columns: S (and P over it) of tile A / B at 0 / 128, the O accumulator at 256 / 384
 __host__ __device__ constexpr int s_col(int t) { return t * 128; }
 __host__ __device__ constexpr int r_col(int t) { return 256 + t * 128; }
 constexpr int ATTN_TMEM_COLS = 512;
@@ -33,7 +35,7 @@ struct AttnBars {
     uint64_t q_full;
     uint64_t k_full[KV_STAGES], k_empty[KV_STAGES];
     uint64_t v_full[KV_STAGES], v_empty[KV_STAGES];
-    uint64_t s_full[2], p_full[2], r_full[2], r_empty[2];
+    uint64_t s_full[2], p_full[2], r_full[2];
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
@@ -82,7 +84,6 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             mbar_init(&bars->s_full[t], 1);
             mbar_init(&bars->p_full[t], 4);
             mbar_init(&bars->r_full[t], 1);
-            mbar_init(&bars->r_empty[t], 4);
         }
         bars->abort_flag = 0;
         mbar_fence_init();
@@ -136,12 +137,12 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                         mma_ss(tmem + s_col(t), smem_desc_kmajor(qa + a * QT * 64 + h * 32, 64),
                                smem_desc_kmajor(ka + a * KT * 64 + h * 32, 64), IDESC_S, (a | h) != 0);
             };
-            auto issue_r = [&](int t, int s) {
+            auto issue_r = [&](int t, int s, bool first) {
                 const uint32_t va = smem_u32(v_smem + s * L::V_TILE);
 #pragma unroll
                 for (int kk = 0; kk < KT / 16; ++kk)
                     mma_ts(tmem + r_col(t), tmem + s_col(t) + kk * 8,
-                           smem_desc_kmajor(va + (kk >> 2) * HD * 128 + (kk & 3) * 32, 128), IDESC_R, kk != 0);
+                           smem_desc_kmajor(va + (kk >> 2) * HD * 128 + (kk & 3) * 32, 128), IDESC_R, !first || kk != 0);
             };
             bool ok = mbar_wait(&bars->q_full, 0, abort_flag, 13);
             if (ok) ok = mbar_wait(&bars->k_full[0], 0, abort_flag, 14);
@@ -162,11 +163,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 if (!mbar_wait(&bars->v_full[s], ph, abort_flag, 15)) { ok = false; break; }
                 if (more && !mbar_wait(&bars->k_full[s1], ph1, abort_flag, 16)) { ok = false; break; }
                 for (int t = 0; t < 2; ++t) {
-                    // P_t(j) is in TMEM and R_t's scratch has been drained of tile j-1
+                    // P_t(j) is in TMEM (and the O row was rescaled if its reference maximum moved)
                     if (!mbar_wait(&bars->p_full[t], jp, abort_flag, 17)) { ok = false; break; }
-                    if (j > 0 && !mbar_wait(&bars->r_empty[t], (j - 1) & 1u, abort_flag, 18)) { ok = false; break; }
                     tc_fence_after();
-                    issue_r(t, s);
+                    issue_r(t, s, j == 0);
                     tc_commit(&bars->r_full[t]);
                     if (more) {
                         issue_s(t, s1);
@@ -179,94 +179,99 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             }
         }
     } else {
-        // ---------------- softmax + accumulate warps ----------------
+        // ---------------- softmax warps ----------------
         const int t = (warp - 2) >> 2;          // query tile A / B
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;    // query row inside the tile
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         const float c = p.scale * 1.4426950408889634f;  // softmax in the exp2 domain
-        float m_run = -INFINITY, l_run = 0.0f, alpha_prev = 1.0f;
-        float o[HD];
-#pragma unroll
-        for (int d = 0; d < HD; ++d) o[d] = 0.0f;
+        float m_ref = -INFINITY, l_run = 0.0f;
         bool ok = true;
-        auto drain = [&](float alpha) {
-#pragma unroll
-            for (int ch = 0; ch < HD / 32; ++ch) {
-                uint32_t v[32];
-                tmem_ld_x32(tmem + lane_addr + r_col(t) + ch * 32, v);
-                tc_wait_ld();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) o[ch * 32 + i] = o[ch * 32 + i] * alpha + __uint_as_float(v[i]);
-            }
-        };
         for (int j = 0; j < nk; ++j) {
-            const uint32_t jp = j & 1u;
-            if (!mbar_wait(&bars->s_full[t], jp, abort_flag, 19)) { ok = false; break; }
+            if (!mbar_wait(&bars->s_full[t], j & 1u, abort_flag, 19)) { ok = false; break; }
             tc_fence_after();
-            if (j > 0) {
-                // R(j-1) finished before S(j) (same issue queue); fold it in and free the scratch
-                if (!mbar_wait(&bars->r_full[t], (j - 1) & 1u, abort_flag, 20)) { ok = false; break; }
-                tc_fence_after();
-                drain(alpha_prev);
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bars->r_empty[t]);
-            }
-            const int kbase = j * KT;
-            const int valid = seg_len - kbase;  // keys of this tile inside the segment
-            // pass 1: row maximum
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int ch = 0; ch < 4; ++ch) {
-                uint32_t v[32];
-                tmem_ld_x32(tmem + lane_addr + s_col(t) + ch * 32, v);
-                tc_wait_ld();
+            // the whole score row of this thread: four loads in flight, one wait
+            uint32_t v[4][32];
 #pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    if (ch * 32 + i < valid) mx = fmaxf(mx, __uint_as_float(v[i]));
+            for (int ch = 0; ch < 4; ++ch) tmem_ld_x32(tmem + lane_addr + s_col(t) + ch * 32, v[ch]);
+            tc_wait_ld();
+            const int valid = seg_len - j * KT;  // keys of this tile inside the segment
+            float mx = -INFINITY;
+            if (valid >= KT) {
+#pragma unroll
+                for (int ch = 0; ch < 4; ++ch)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[ch][i]));
+            } else {
+#pragma unroll
+                for (int ch = 0; ch < 4; ++ch)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        if (ch * 32 + i >= valid) v[ch][i] = 0xff800000u;  // -inf: exp2 gives 0
+                        mx = fmaxf(mx, __uint_as_float(v[ch][i]));
+                    }
             }
-            const float m_new = fmaxf(m_run, mx * c);
-            alpha_prev = exp2f(m_run - m_new);  // 0 on the first tile (m_run = -inf)
-            float sum = 0.0f;
-            // pass 2: probabilities, packed to bf16 over the S columns already consumed
+            const float m_cand = mx * c;
+            const bool moved = m_cand > m_ref + 8.0f;  // always true on the first tile
+            if (__any_sync(0xffffffffu, moved)) {
+                // s_full(j) is signalled after every earlier MMA of this tile finished, P V of tile
+                // j-1 included, and P V of tile j is not issued before this thread arrives on
+                // p_full: the O row can be rescaled in place.
+                const float alpha = moved ? ex2_approx(m_ref - m_cand) : 1.0f;
+                if (moved) m_ref = m_cand;
+                l_run *= alpha;
+                if (j > 0) {
+                    // rare path, small chunks: the score row stays live in registers meanwhile
 #pragma unroll 1
+                    for (int ch = 0; ch < HD / 8; ++ch) {
+                        uint32_t o[8];
+                        tmem_ld_x8(tmem + lane_addr + r_col(t) + ch * 8, o);
+                        tc_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st_x8(tmem + lane_addr + r_col(t) + ch * 8, o);
+                    }
+                }
+            }
+            float sum = 0.0f;
+#pragma unroll
             for (int ch = 0; ch < 4; ++ch) {
-                uint32_t v[32];
-                tmem_ld_x32(tmem + lane_addr + s_col(t) + ch * 32, v);
-                tc_wait_ld();
                 uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    float e0 = (ch * 32 + i < valid) ? exp2f(__uint_as_float(v[i]) * c - m_new) : 0.0f;
-                    float e1 = (ch * 32 + i + 1 < valid) ? exp2f(__uint_as_float(v[i + 1]) * c - m_new) : 0.0f;
+                    const float e0 = ex2_approx(fmaf(__uint_as_float(v[ch][i]), c, -m_ref));
+                    const float e1 = ex2_approx(fmaf(__uint_as_float(v[ch][i + 1]), c, -m_ref));
                     sum += e0 + e1;
                     pk[i >> 1] = pack_bf16(e0, e1);
                 }
                 tmem_st_x16(tmem + lane_addr + s_col(t) + ch * 16, pk);
             }
             tc_wait_st();
-            l_run = l_run * alpha_prev + sum;
-            m_run = m_new;
+            l_run += sum;
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars->p_full[t]);
         }
         if (ok && mbar_wait(&bars->r_full[t], (nk - 1) & 1u, abort_flag, 21)) {
             tc_fence_after();
-            drain(alpha_prev);
             const int qrow = q0 + t * QT + row;
-            if (qrow < seg_len) {
-                const float inv = 1.0f / l_run;
-                __nv_bfloat16* dst = p.out + ((size_t)(seg0 + qrow) * p.nh + head) * HD;
+            const float inv = 1.0f / l_run;
+            __nv_bfloat16* dst = p.out + ((size_t)(seg0 + qrow) * p.nh + head) * HD;
 #pragma unroll
-                for (int d = 0; d < HD; d += 8) {
-                    uint4 w;
-                    w.x = pack_bf16(o[d] * inv, o[d + 1] * inv);
-                    w.y = pack_bf16(o[d + 2] * inv, o[d + 3] * inv);
-                    w.z = pack_bf16(o[d + 4] * inv, o[d + 5] * inv);
-                    w.w = pack_bf16(o[d + 6] * inv, o[d + 7] * inv);
-                    *reinterpret_cast<uint4*>(dst + d) = w;
+            for (int ch = 0; ch < HD / 32; ++ch) {
+                uint32_t o[32];
+                tmem_ld_x32(tmem + lane_addr + r_col(t) + ch * 32, o);
+                tc_wait_ld();
+                if (qrow < seg_len) {
+#pragma unroll
+                    for (int d = 0; d < 32; d += 8) {
+                        uint4 w;
+                        w.x = pack_bf16(__uint_as_float(o[d]) * inv, __uint_as_float(o[d + 1]) * inv);
+                        w.y = pack_bf16(__uint_as_float(o[d + 2]) * inv, __uint_as_float(o[d + 3]) * inv);
+                        w.z = pack_bf16(__uint_as_float(o[d + 4]) * inv, __uint_as_float(o[d + 5]) * inv);
+                        w.w = pack_bf16(__uint_as_float(o[d + 6]) * inv, __uint_as_float(o[d + 7]) * inv);
+                        *reinterpret_cast<uint4*>(dst + ch * 32 + d) = w;
+                    }
                 }
             }
         }

@@ -42,7 +42,8 @@ int fail(int code, const std::string& msg);
 
 // Device-side wait budget: polls of mbarrier.try_wait before a kernel gives up, records the
 // site in its status word and leaves through the normal exit path.
-constexpr uint32_t WAIT_POLLS = 1u << 22;
+constexpr uint32_t WAIT_POLLS = 1u << 18;
+constexpr uint32_t WAIT_PARK_NS = 8000;
 
 #ifdef __CUDACC__
 
@@ -89,13 +90,30 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Same, but the hardware may park the thread for up to ``hint_ns`` while the phase is pending,
+// so a waiting warp does not compete for issue slots with the warps doing the work.
+__device__ __forceinline__ bool mbar_try_parked(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait.  Returns false when the budget ran out or another thread already flagged an
 // abort (``abort_flag`` lives in shared memory); the caller then unwinds to the common exit.
+// Budget: WAIT_POLLS parked polls of up to WAIT_PARK_NS each (about two seconds).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
                                           uint32_t site) {
+    if (mbar_try(bar, parity)) return true;
     for (uint32_t i = 0; i < WAIT_POLLS; ++i) {
-        if (mbar_try(bar, parity)) return true;
-        if ((i & 1023u) == 1023u && *abort_flag) return false;
+        if (mbar_try_parked(bar, parity, WAIT_PARK_NS)) return true;
+        if ((i & 63u) == 63u && *abort_flag) return false;
     }
     atomicCAS(const_cast<uint32_t*>(abort_flag), 0u, site);
     return false;
@@ -200,6 +218,17 @@ __device__ __forceinline__ void tmem_ld_x32(uint32_t taddr, uint32_t (&r)[32]) {
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ void tmem_ld_x8(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st_x8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]),
+                 "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
 __device__ __forceinline__ void tmem_st_x16(uint32_t taddr, const uint32_t (&r)[16]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
@@ -225,6 +254,13 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     uint32_t r;
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
     return r;
+}
+
+// 2^x on the special-function unit (ex2.approx: relative error about 2^-22; -inf gives 0)
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 
 __device__ __forceinline__ float warp_sum(float v) {

@@ -6,15 +6,16 @@
 // The product is computed transposed, D[n, m] = W[n, :] . X[m, :], so that the dequantized
 // weights are the tcgen05 A operand (one weight row per TMEM lane) and the activations are
 // the B operand:
-//   * X (bf16, K-major) tiles of 256 tokens x 64 k arrive by TMA with the 128-byte swizzle
+//   * X (bf16, K-major) tiles of 192 tokens x 64 k arrive by TMA with the 128-byte swizzle
 //     and are consumed by the tensor core straight from shared memory;
 //   * the packed weight tile of 128 rows x 64 k (int8, or 4-bit nibbles plus a per-group f32
 //     scale) arrives by TMA as raw bytes; eight dequant warps, one weight row per thread,
 //     unpack it in registers to bf16 and write it to TENSOR MEMORY with tcgen05.st;
-//   * one elected thread issues tcgen05.mma (A from TMEM, B from SMEM, 128 x 256 x 16) into a
-//     256-column f32 accumulator in TMEM;
-//   * the same eight warps drain the accumulator with tcgen05.ld and store Y (f32 or bf16, or
-//     the fused SwiGLU product when the weight rows interleave W1 and W3).
+//   * one elected thread issues tcgen05.mma (A from TMEM, B from SMEM, 128 x 192 x 16) into one
+//     of TWO 192-column f32 accumulators in TMEM (2 x 192 + 4 x 32 columns of A = 512);
+//   * four epilogue warps drain the finished accumulator with tcgen05.ld and store Y (f32 or
+//     bf16, or the fused SwiGLU product when the weight rows interleave W1 and W3) while the
+//     tensor core already works on the next tile in the other accumulator.
 // Persistent: grid = min(#tiles, #SMs); each CTA walks tiles blockIdx.x, +gridDim.x, ...
 //
 // bf16 operand definition: RN_bf16(exact f32 dequantized weight).  For q8 the integer level
@@ -26,25 +27,28 @@ namespace cmfc {
 namespace {
 
 constexpr int TW = 128;     // weight rows per tile  (UMMA M, TMEM lanes)
-constexpr int TT = 256;     // tokens per tile       (UMMA N, accumulator columns)
+constexpr int TT = 192;     // tokens per tile       (UMMA N, accumulator columns)
 constexpr int BK = 64;      // k per pipeline stage  (one 128-byte swizzle atom of bf16)
-constexpr int STAGES = 4;
-constexpr int X_STAGE = TT * BK * 2;   // 32 KiB
+constexpr int STAGES = 6;    // shared-memory ring (X tile + packed W tile + scales)
+constexpr int ASTAGES = 4;   // tensor-memory ring of dequantized A tiles
+constexpr int X_STAGE = TT * BK * 2;   // 24 KiB
 constexpr int W_STAGE = TW * BK;       // 8 KiB (q8: 64 B/row; q4 uses the first 4 KiB)
 constexpr int S_STAGE = 2 * TW * 4;    // 1 KiB (q4: two groups x 128 rows of f32 scales)
-constexpr int ACC_COL = 0;
-constexpr int A_COL = 256;             // four A stages of 32 columns (64 bf16) each
+constexpr int A_COL = 2 * TT;          // after the two accumulators: four A stages of 32 columns
 constexpr int TMEM_COLS = 512;
 constexpr int NUM_DQ_WARPS = 8;
-constexpr int THREADS = 32 * (2 + NUM_DQ_WARPS);
+constexpr int NUM_EPI_WARPS = 4;
+constexpr int THREADS = 32 * (2 + NUM_DQ_WARPS + NUM_EPI_WARPS);
+static_assert(A_COL + ASTAGES * 32 <= TMEM_COLS, "TMEM budget");
 constexpr int SMEM_BYTES = STAGES * (X_STAGE + W_STAGE + S_STAGE) + 1024 /*align*/ + 256 /*barriers*/;
 
 struct Bars {
     uint64_t full[STAGES];
     uint64_t empty[STAGES];
-    uint64_t a_full[STAGES];
-    uint64_t acc_full;
-    uint64_t acc_empty;
+    uint64_t a_full[ASTAGES];
+    uint64_t a_empty[ASTAGES];
+    uint64_t acc_full[2];
+    uint64_t acc_empty[2];
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
@@ -106,7 +110,10 @@ gemm_dequant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     const int lane = threadIdx.x & 31;
     const int kblocks = p.K / BK;
     const int tiles_m = (p.M + TT - 1) / TT;
-    const int tiles = tiles_m * (p.N / TW);
+    // Tile order: consecutive tiles share the token tile, so the CTAs running at one time read the
+    // same X rows (served by L2 after the first) while the small packed weights stay L2 resident.
+    const int tiles_n = p.N / TW;
+    const int tiles = tiles_m * tiles_n;
     constexpr uint32_t W_BYTES = (WKIND == 0) ? TW * BK : TW * BK / 2;
     constexpr uint32_t TX_BYTES = X_STAGE + W_BYTES + (WKIND == 1 ? S_STAGE : 0);
 
@@ -114,10 +121,15 @@ gemm_dequant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&bars->full[s], 1);
             mbar_init(&bars->empty[s], 1 + NUM_DQ_WARPS);
-            mbar_init(&bars->a_full[s], NUM_DQ_WARPS);
         }
-        mbar_init(&bars->acc_full, 1);
-        mbar_init(&bars->acc_empty, NUM_DQ_WARPS);
+        for (int a = 0; a < ASTAGES; ++a) {
+            mbar_init(&bars->a_full[a], NUM_DQ_WARPS);
+            mbar_init(&bars->a_empty[a], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&bars->acc_full[b], 1);
+            mbar_init(&bars->acc_empty[b], NUM_EPI_WARPS);
+        }
         bars->abort_flag = 0;
         mbar_fence_init();
         tma_prefetch_desc(&tm_x);
@@ -138,7 +150,7 @@ gemm_dequant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         if (elect_one()) {
             uint32_t it = 0;
             for (int tile = blockIdx.x; tile < tiles && !*abort_flag; tile += gridDim.x) {
-                const int n0 = (tile / tiles_m) * TW, m0 = (tile % tiles_m) * TT;
+                const int n0 = (tile % tiles_n) * TW, m0 = (tile / tiles_n) * TT;
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1u;
@@ -160,41 +172,55 @@ gemm_dequant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
             constexpr uint32_t IDESC = idesc_bf16_f32(TW, TT);
             uint32_t it = 0, tile_i = 0;
             for (int tile = blockIdx.x; tile < tiles && !*abort_flag; tile += gridDim.x, ++tile_i) {
-                if (tile_i > 0 && !mbar_wait(&bars->acc_empty, (tile_i - 1) & 1u, abort_flag, 2)) break;
+                const uint32_t buf = tile_i & 1u, acc = tmem + buf * TT;
+                // the epilogue warps must have drained this accumulator's previous tile
+                if (!mbar_wait(&bars->acc_empty[buf], ((tile_i >> 1) & 1u) ^ 1u, abort_flag, 2)) break;
                 tc_fence_after();
                 bool ok = true;
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
-                    const int s = it % STAGES;
-                    const uint32_t ph = (it / STAGES) & 1u;
+                    const int s = it % STAGES, ai = it % ASTAGES;
+                    const uint32_t ph = (it / STAGES) & 1u, aph = (it / ASTAGES) & 1u;
                     if (!mbar_wait(&bars->full[s], ph, abort_flag, 3) ||
-                        !mbar_wait(&bars->a_full[s], ph, abort_flag, 4)) { ok = false; break; }
+                        !mbar_wait(&bars->a_full[ai], aph, abort_flag, 4)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t xs = smem_u32(x_smem + s * X_STAGE);
 #pragma unroll
                     for (int j = 0; j < BK / 16; ++j) {
-                        mma_ts(tmem + ACC_COL, tmem + A_COL + s * 32 + j * 8, smem_desc_kmajor(xs + j * 32, 128),
+                        mma_ts(acc, tmem + A_COL + ai * 32 + j * 8, smem_desc_kmajor(xs + j * 32, 128),
                                IDESC, (kb | j) != 0);
                     }
                     tc_commit(&bars->empty[s]);
+                    tc_commit(&bars->a_empty[ai]);
                 }
                 if (!ok) break;
-                tc_commit(&bars->acc_full);
+                tc_commit(&bars->acc_full[buf]);
             }
         }
-    } else {
-        // ---------------- dequant + epilogue warps ----------------
+    } else if (warp < 2 + NUM_DQ_WARPS) {
+        // ---------------- dequant warps ----------------
         const int dq = warp - 2;                 // 0..7
         const int quarter = warp & 3;            // TMEM lane quarter this warp may touch
-        const int half = dq >> 2;                // which 32 k of the 64-k stage / which 128 tokens
+        const int half = dq >> 2;                // which 32 k of the 64-k stage
         const int row = quarter * 32 + lane;     // weight row inside the tile
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-        uint32_t it = 0, tile_i = 0;
+        uint32_t it = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < tiles && ok && !*abort_flag; tile += gridDim.x, ++tile_i) {
-            const int n0 = (tile / tiles_m) * TW, m0 = (tile % tiles_m) * TT;
+        int pending = -1;  // A stage whose tcgen05.st is still in flight
+        // Software pipeline: the TMEM store of k-block i is left in flight while k-block i+1 is
+        // unpacked; a_full[i] is signalled once that store has completed.
+        auto flush = [&]() {
+            if (pending >= 0) {
+                tc_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars->a_full[pending]);
+                pending = -1;
+            }
+        };
+        for (int tile = blockIdx.x; tile < tiles && ok && !*abort_flag; tile += gridDim.x) {
             for (int kb = 0; kb < kblocks; ++kb, ++it) {
-                const int s = it % STAGES;
-                const uint32_t ph = (it / STAGES) & 1u;
+                const int s = it % STAGES, ai = it % ASTAGES;
+                const uint32_t ph = (it / STAGES) & 1u, aph = (it / ASTAGES) & 1u;
                 if (!mbar_wait(&bars->full[s], ph, abort_flag, 5)) { ok = false; break; }
                 uint32_t a[16];
                 if (WKIND == 0) {
@@ -217,30 +243,39 @@ gemm_dequant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
                     unpack_q4_word(v.z, q, a + 8);
                     unpack_q4_word(v.w, q, a + 12);
                 }
-                // The previous occupant of A stage s was consumed before full[s] could fire
-                // again (the producer refills a stage only after the MMAs on it committed).
-                tmem_st_x16(tmem + lane_addr + A_COL + s * 32 + half * 16, a);
-                tc_wait_st();
-                tc_fence_before();
                 __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(&bars->a_full[s]);
-                    mbar_arrive(&bars->empty[s]);
-                }
+                if (lane == 0) mbar_arrive(&bars->empty[s]);  // the packed bytes are in registers
+                flush();
+                // A stage ai is free once the MMAs that read its previous tile have committed
+                if (!mbar_wait(&bars->a_empty[ai], aph ^ 1u, abort_flag, 7)) { ok = false; break; }
+                tc_fence_after();
+                tmem_st_x16(tmem + lane_addr + A_COL + ai * 32 + half * 16, a);
+                pending = ai;
             }
-            if (!ok) break;
-            // ---- epilogue: this thread owns output channel n0+row, tokens m0+128*half+[0,128) ----
-            if (!mbar_wait(&bars->acc_full, tile_i & 1u, abort_flag, 6)) { ok = false; break; }
+        }
+        flush();
+    } else {
+        // ---------------- epilogue warps ----------------
+        // This thread owns output channel n0+row and all TT tokens of the tile.
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        uint32_t tile_i = 0;
+        for (int tile = blockIdx.x; tile < tiles && !*abort_flag; tile += gridDim.x, ++tile_i) {
+            const int n0 = (tile % tiles_n) * TW, m0 = (tile / tiles_n) * TT;
+            const uint32_t buf = tile_i & 1u;
+            if (!mbar_wait(&bars->acc_full[buf], (tile_i >> 1) & 1u, abort_flag, 6)) break;
             tc_fence_after();
             const int n = n0 + row;
             float rs = 1.0f;
             if (WKIND == 0) rs = p.row_scale[n];
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < TT / 32; ++c) {
                 uint32_t v[32];
-                tmem_ld_x32(tmem + lane_addr + ACC_COL + half * 128 + c * 32, v);
+                tmem_ld_x32(tmem + lane_addr + buf * TT + c * 32, v);
                 tc_wait_ld();
-                const int mb = m0 + half * 128 + c * 32;
+                const int mb = m0 + c * 32;
+                if (mb >= p.M) break;
                 if (p.mode == GEMM_OUT_F32) {
                     float* out = reinterpret_cast<float*>(p.out) + (size_t)mb * p.ldo + n;
 #pragma unroll
@@ -270,7 +305,7 @@ gemm_dequant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&bars->acc_empty);
+            if (lane == 0) mbar_arrive(&bars->acc_empty[buf]);
         }
     }
 
