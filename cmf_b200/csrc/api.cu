@@ -910,7 +910,7 @@ extern "C" uint64_t cmfc_launch_count(int reset) {
 
 extern "C" int cmfc_bench_gemm(cmfc_model* m, int64_t idx, size_t M, int mode, int iters, float* ms_per_launch) {
     NEED(m && ms_per_launch && M > 0 && iters > 0, "bench_gemm: bad argument");
-    NEED(mode == GEMM_OUT_F32 || mode == GEMM_OUT_BF16, "bench_gemm: mode must be 0 (f32) or 1 (bf16)");
+    NEED(mode >= GEMM_OUT_F32 && mode <= GEMM_OUT_SWIGLU, "bench_gemm: mode must be 0 (f32), 1 (bf16) or 2 (SwiGLU pairs)");
     NEED_CTX();
     DevWeight* w = nullptr;
     CMFC_TRY(get_weight(c, m->m, idx, &w));
@@ -921,12 +921,13 @@ extern "C" int cmfc_bench_gemm(cmfc_model* m, int64_t idx, size_t M, int mode, i
     launch_fill_normal(xf.as<float>(), M * w->cols, 1234, 1.0f, c->stream);
     launch_f32_to_bf16(xf.as<float>(), xb.as<__nv_bfloat16>(), M * w->cols, c->stream);
     c->launches += 2;
-    for (int i = 0; i < 3; ++i) CMFC_TRY(dev_gemm(c, w, xb.as<__nv_bfloat16>(), (int)M, y.p, w->rows, mode));
+    const int ldo = mode == GEMM_OUT_SWIGLU ? w->rows / 2 : w->rows;
+    for (int i = 0; i < 3; ++i) CMFC_TRY(dev_gemm(c, w, xb.as<__nv_bfloat16>(), (int)M, y.p, ldo, mode));
     cudaEvent_t e0, e1;
     CMFC_CUDA(cudaEventCreate(&e0));
     CMFC_CUDA(cudaEventCreate(&e1));
     CMFC_CUDA(cudaEventRecord(e0, c->stream));
-    for (int i = 0; i < iters; ++i) CMFC_TRY(dev_gemm(c, w, xb.as<__nv_bfloat16>(), (int)M, y.p, w->rows, mode));
+    for (int i = 0; i < iters; ++i) CMFC_TRY(dev_gemm(c, w, xb.as<__nv_bfloat16>(), (int)M, y.p, ldo, mode));
     CMFC_CUDA(cudaEventRecord(e1, c->stream));
     CMFC_CUDA(cudaEventSynchronize(e1));
     float ms = 0;

@@ -111,12 +111,12 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             for (int j = 0; j < nk; ++j) {
                 const int s = j % KV_STAGES;
                 const uint32_t ph = (j / KV_STAGES) & 1u;
-                if (!mbar_wait(&bars->k_empty[s], ph ^ 1u, abort_flag, 11)) break;
+                if (!mbar_wait<200>(&bars->k_empty[s], ph ^ 1u, abort_flag, 11)) break;
                 mbar_expect_tx(&bars->k_full[s], L::K_TILE);
                 for (int a = 0; a < L::ATOMS; ++a)
                     tma_load_2d(k_smem + s * L::K_TILE + a * KT * 64, &tm_k, &bars->k_full[s], kvh * HD + 32 * a,
                                 seg0 + j * KT);
-                if (!mbar_wait(&bars->v_empty[s], ph ^ 1u, abort_flag, 12)) break;
+                if (!mbar_wait<200>(&bars->v_empty[s], ph ^ 1u, abort_flag, 12)) break;
                 mbar_expect_tx(&bars->v_full[s], L::V_TILE);
                 for (int b = 0; b < 2; ++b)
                     tma_load_2d(v_smem + s * L::V_TILE + b * HD * 128, &tm_vt, &bars->v_full[s], vt0 + j * KT + 64 * b,
@@ -188,7 +188,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         float m_ref = -INFINITY, l_run = 0.0f;
         bool ok = true;
         for (int j = 0; j < nk; ++j) {
-            if (!mbar_wait(&bars->s_full[t], j & 1u, abort_flag, 19)) { ok = false; break; }
+            if (!mbar_wait<60>(&bars->s_full[t], j & 1u, abort_flag, 19)) { ok = false; break; }
             tc_fence_after();
             // the whole score row of this thread: four loads in flight, one wait
             uint32_t v[4][32];

@@ -107,12 +107,17 @@ __device__ __forceinline__ bool mbar_try_parked(uint64_t* bar, uint32_t parity, 
 }
 // Bounded wait.  Returns false when the budget ran out or another thread already flagged an
 // abort (``abort_flag`` lives in shared memory); the caller then unwinds to the common exit.
-// Budget: WAIT_POLLS parked polls of up to WAIT_PARK_NS each (about two seconds).
+// ``nap_ns`` > 0 makes a waiter that is not on the critical path sleep between polls, so it
+// leaves the issue slots of its scheduler to the warps doing the work.  The budget is about two
+// seconds either way.
+template <uint32_t NAP_NS = 0>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
                                           uint32_t site) {
     if (mbar_try(bar, parity)) return true;
-    for (uint32_t i = 0; i < WAIT_POLLS; ++i) {
-        if (mbar_try_parked(bar, parity, WAIT_PARK_NS)) return true;
+    constexpr uint32_t polls = NAP_NS ? (2000000000u / (NAP_NS + 200u)) : WAIT_POLLS;
+    for (uint32_t i = 0; i < polls; ++i) {
+        if (NAP_NS) __nanosleep(NAP_NS);
+        if (NAP_NS ? mbar_try(bar, parity) : mbar_try_parked(bar, parity, WAIT_PARK_NS)) return true;
         if ((i & 63u) == 63u && *abort_flag) return false;
     }
     atomicCAS(const_cast<uint32_t*>(abort_flag), 0u, site);

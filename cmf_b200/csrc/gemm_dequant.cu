@@ -6,16 +6,17 @@
 // The product is computed transposed, D[n, m] = W[n, :] . X[m, :], so that the dequantized
 // weights are the tcgen05 A operand (one weight row per TMEM lane) and the activations are
 // the B operand:
-//   * X (bf16, K-major) tiles of 192 tokens x 64 k arrive by TMA with the 128-byte swizzle
+//   * X (bf16, K-major) tiles of 256 tokens x 64 k arrive by TMA with the 128-byte swizzle
 //     and are consumed by the tensor core straight from shared memory;
 //   * the packed weight tile of 128 rows x 64 k (int8, or 4-bit nibbles plus a per-group f32
 //     scale) arrives by TMA as raw bytes; eight dequant warps, one weight row per thread,
 //     unpack it in registers to bf16 and write it to TENSOR MEMORY with tcgen05.st;
-//   * one elected thread issues tcgen05.mma (A from TMEM, B from SMEM, 128 x 192 x 16) into one
-//     of TWO 192-column f32 accumulators in TMEM (2 x 192 + 4 x 32 columns of A = 512);
+//   * one elected thread issues tcgen05.mma (A from TMEM, B from SMEM, 128 x 256 x 16) into a
+//     256-column f32 accumulator in TMEM; the other 256 columns are an 8-deep ring of A tiles,
+//     so the dequant warps run up to 8 k-blocks ahead of the tensor core;
 //   * four epilogue warps drain the finished accumulator with tcgen05.ld and store Y (f32 or
 //     bf16, or the fused SwiGLU product when the weight rows interleave W1 and W3) while the
-//     tensor core already works on the next tile in the other accumulator.
+//     dequant warps already fill the A ring for the next tile.
 // Persistent: grid = min(#tiles, #SMs); each CTA walks tiles blockIdx.x, +gridDim.x, ...
 //
 // bf16 operand definition: RN_bf16(exact f32 dequantized weight).  For q8 the integer level
@@ -27,17 +28,18 @@ namespace cmfc {
 namespace {
 
 constexpr int TW = 128;     // weight rows per tile  (UMMA M, TMEM lanes)
-constexpr int TT = 192;     // tokens per tile       (UMMA N, accumulator columns)
+constexpr int TT = 256;     // tokens per tile       (UMMA N, accumulator columns)
 constexpr int BK = 64;      // k per pipeline stage  (one 128-byte swizzle atom of bf16)
-constexpr int STAGES = 6;    // shared-memory ring (X tile + packed W tile + scales)
-constexpr int ASTAGES = 4;   // tensor-memory ring of dequantized A tiles
-constexpr int X_STAGE = TT * BK * 2;   // 24 KiB
+constexpr int STAGES = 5;    // shared-memory ring (X tile + packed W tile + scales)
+constexpr int ASTAGES = 8;   // tensor-memory ring of dequantized A tiles
+constexpr int NACC = 1;      // accumulators in TMEM (NACC * TT + ASTAGES * 32 <= 512 columns)
+constexpr int X_STAGE = TT * BK * 2;   // 32 KiB
 constexpr int W_STAGE = TW * BK;       // 8 KiB (q8: 64 B/row; q4 uses the first 4 KiB)
 constexpr int S_STAGE = 2 * TW * 4;    // 1 KiB (q4: two groups x 128 rows of f32 scales)
-constexpr int A_COL = 2 * TT;          // after the two accumulators: four A stages of 32 columns
+constexpr int A_COL = NACC * TT;       // after the accumulator(s): the A ring, 32 columns per stage
 constexpr int TMEM_COLS = 512;
 constexpr int NUM_DQ_WARPS = 8;
-constexpr int NUM_EPI_WARPS = 4;
+constexpr int NUM_EPI_WARPS = 8;
 constexpr int THREADS = 32 * (2 + NUM_DQ_WARPS + NUM_EPI_WARPS);
 static_assert(A_COL + ASTAGES * 32 <= TMEM_COLS, "TMEM budget");
 constexpr int SMEM_BYTES = STAGES * (X_STAGE + W_STAGE + S_STAGE) + 1024 /*align*/ + 256 /*barriers*/;
@@ -92,7 +94,7 @@ __device__ __forceinline__ void unpack_q4_word(uint32_t w, const Q4Scales& sc, u
 
 __device__ __forceinline__ uint4 lds128(const uint8_t* p) { return *reinterpret_cast<const uint4*>(p); }
 
-__device__ __forceinline__ float silu_f(float v) { return v / (1.0f + __expf(-v)); }
+__device__ __forceinline__ float silu_f(float v) { return __fdividef(v, 1.0f + __expf(-v)); }
 
 template <int WKIND>  // 0 = q8 (int8 plane), 1 = q4 (nibble plane + transposed f32 scales)
 __global__ void __launch_bounds__(THREADS, 1)
@@ -154,7 +156,7 @@ gemm_dequant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1u;
-                    if (!mbar_wait(&bars->empty[s], ph ^ 1u, abort_flag, 1)) break;
+                    if (!mbar_wait<200>(&bars->empty[s], ph ^ 1u, abort_flag, 1)) break;
                     mbar_expect_tx(&bars->full[s], TX_BYTES);
                     tma_load_2d(x_smem + s * X_STAGE, &tm_x, &bars->full[s], kb * BK, m0);
                     if (WKIND == 0) {
@@ -172,9 +174,9 @@ gemm_dequant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
             constexpr uint32_t IDESC = idesc_bf16_f32(TW, TT);
             uint32_t it = 0, tile_i = 0;
             for (int tile = blockIdx.x; tile < tiles && !*abort_flag; tile += gridDim.x, ++tile_i) {
-                const uint32_t buf = tile_i & 1u, acc = tmem + buf * TT;
+                const uint32_t buf = tile_i % NACC, acc = tmem + buf * TT;
                 // the epilogue warps must have drained this accumulator's previous tile
-                if (!mbar_wait(&bars->acc_empty[buf], ((tile_i >> 1) & 1u) ^ 1u, abort_flag, 2)) break;
+                if (!mbar_wait(&bars->acc_empty[buf], ((tile_i / NACC) & 1u) ^ 1u, abort_flag, 2)) break;
                 tc_fence_after();
                 bool ok = true;
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
@@ -221,7 +223,7 @@ gemm_dequant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
             for (int kb = 0; kb < kblocks; ++kb, ++it) {
                 const int s = it % STAGES, ai = it % ASTAGES;
                 const uint32_t ph = (it / STAGES) & 1u, aph = (it / ASTAGES) & 1u;
-                if (!mbar_wait(&bars->full[s], ph, abort_flag, 5)) { ok = false; break; }
+                if (!mbar_wait<100>(&bars->full[s], ph, abort_flag, 5)) { ok = false; break; }
                 uint32_t a[16];
                 if (WKIND == 0) {
                     const uint8_t* wrow = w_smem + s * W_STAGE + row * 64;
@@ -247,7 +249,7 @@ gemm_dequant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
                 if (lane == 0) mbar_arrive(&bars->empty[s]);  // the packed bytes are in registers
                 flush();
                 // A stage ai is free once the MMAs that read its previous tile have committed
-                if (!mbar_wait(&bars->a_empty[ai], aph ^ 1u, abort_flag, 7)) { ok = false; break; }
+                if (!mbar_wait<100>(&bars->a_empty[ai], aph ^ 1u, abort_flag, 7)) { ok = false; break; }
                 tc_fence_after();
                 tmem_st_x16(tmem + lane_addr + A_COL + ai * 32 + half * 16, a);
                 pending = ai;
@@ -256,21 +258,22 @@ gemm_dequant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         flush();
     } else {
         // ---------------- epilogue warps ----------------
-        // This thread owns output channel n0+row and all TT tokens of the tile.
+        // This thread owns output channel n0+row and half of the tile's tokens.
         const int quarter = warp & 3;
+        const int ehalf = (warp - 2 - NUM_DQ_WARPS) >> 2;
         const int row = quarter * 32 + lane;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         uint32_t tile_i = 0;
         for (int tile = blockIdx.x; tile < tiles && !*abort_flag; tile += gridDim.x, ++tile_i) {
             const int n0 = (tile % tiles_n) * TW, m0 = (tile / tiles_n) * TT;
-            const uint32_t buf = tile_i & 1u;
-            if (!mbar_wait(&bars->acc_full[buf], (tile_i >> 1) & 1u, abort_flag, 6)) break;
+            const uint32_t buf = tile_i % NACC;
+            if (!mbar_wait<(NACC > 1 ? 1000 : 80)>(&bars->acc_full[buf], (tile_i / NACC) & 1u, abort_flag, 6)) break;
             tc_fence_after();
             const int n = n0 + row;
             float rs = 1.0f;
             if (WKIND == 0) rs = p.row_scale[n];
 #pragma unroll 1
-            for (int c = 0; c < TT / 32; ++c) {
+            for (int c = ehalf * (TT / 64); c < (ehalf + 1) * (TT / 64); ++c) {
                 uint32_t v[32];
                 tmem_ld_x32(tmem + lane_addr + buf * TT + c * 32, v);
                 tc_wait_ld();

@@ -35,7 +35,7 @@ def gemm(codec, N, K, M, iters, mode=0):
     finally:
         os.remove(path)
     bpw = {"q8": 1.0, "q4t": 0.5625, "q4tp": 0.5195}[codec]
-    return {"kernel": "gemm_dequant", "codec": codec, "M": M, "N": N, "K": K, "ms": ms,
+    return {"kernel": "gemm_dequant", "codec": codec, "mode": mode, "M": M, "N": N, "K": K, "ms": ms,
             "tflops": 2.0 * M * N * K / (ms * 1e-3) / 1e12,
             "algorithmic_bytes": K * N * bpw + 2.0 * M * K + (4.0 if mode == 0 else 2.0) * M * N}
 
@@ -52,11 +52,12 @@ def main():
     ap.add_argument("--rows", type=int, default=8704)
     ap.add_argument("--cols", type=int, default=2304)
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--mode", type=int, default=0, help="GEMM output: 0 f32, 1 bf16, 2 fused SwiGLU pairs")
     ap.add_argument("--device", type=int, default=0)
     a = ap.parse_args()
     gpu.set_current_device(a.device)
     if a.what == "gemm":
-        print(json.dumps(gemm(a.codec, a.N, a.K, a.M, a.iters)))
+        print(json.dumps(gemm(a.codec, a.N, a.K, a.M, a.iters, a.mode)))
     elif a.what == "attention":
         ms = gpu.bench_attention(24, 8, 96, a.n, a.nseg, a.iters)
         fl = 4.0 * a.n * a.n * 24 * 96 * a.nseg
