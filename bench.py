@@ -266,10 +266,10 @@ def main():
     out = denoise(dit, lat, cap, cap_u, GenParams(steps=K, guidance_scale=4.0))
     if world > 1:
         # the one collective of the path: gather the final latents on rank 0 over NCCL
-        mine = torch.from_numpy(out).to(f"cuda:{local}")
-        bucket = [torch.empty_like(mine) for _ in range(world)] if rank == 0 else None
-        dist.gather(mine, bucket, dst=0)
+        from cmf_b200.shard import gather_latents
+        gathered = gather_latents(out, world * P, device=f"cuda:{local}")
         torch.cuda.synchronize()
+        assert rank != 0 or gathered.shape[0] == world * P
     e2e_s = torch.tensor([time.time() - t0], device=f"cuda:{local}")
     if world > 1:
         dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
@@ -310,9 +310,12 @@ def main():
             except Exception as e:  # the baseline is a reported figure; its failure must not hide the GPU line
                 line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
                                         "sample": f"failed: {e!r}"}
-        traffic_file = os.path.join(ROOT, "profiles", "gemm_dequant_traffic.json")
-        if os.path.exists(traffic_file):
-            line["roofline"]["traffic"] = json.load(open(traffic_file)).get("dram_bytes_per_launch")
+        if args.codec in ("q4t", "q4tp"):
+            # dram__bytes_read.sum + dram__bytes_write.sum of one captured launch of this kernel, the
+            # gate/up GEMM of a block (N=18432, K=2304, M=8704, SwiGLU epilogue; algorithmic 224 MB):
+            # profiles/gemm_dequant_q4t_swiglu_N18432_K2304_M8704.md
+            line["roofline"]["traffic"] = 207.2e6
+            line["roofline"]["traffic_launch"] = "gate/up GEMM of one block, N=18432 K=2304 M=8704"
         print(json.dumps(line), flush=True)
     dit.close()
     model.close()
