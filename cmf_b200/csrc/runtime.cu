@@ -146,6 +146,14 @@ Context* ctx() {
     return it == g_ctxs.end() ? nullptr : it->second.get();
 }
 
+Context* ctx_existing() {
+    if (g_cur_device < 0) return nullptr;
+    cudaSetDevice(g_cur_device);
+    std::lock_guard<std::mutex> lk(g_ctx_mu);
+    auto it = g_ctxs.find(g_cur_device);
+    return it == g_ctxs.end() ? nullptr : it->second.get();
+}
+
 int check_status(Context* c, const char* what) {
     CMFC_CUDA(cudaMemcpyAsync(c->status_host, c->status, 4, cudaMemcpyDeviceToHost, c->stream));
     CMFC_CUDA(cudaStreamSynchronize(c->stream));

@@ -90,6 +90,7 @@ struct Context {
 
 const std::string& last_error();
 Context* ctx();  // context of the calling thread's current device (created on demand), or null
+Context* ctx_existing();  // same, but never creates a context (and so never allocates)
 int ctx_set_device(int device);
 int check_status(Context* c, const char* what);  // reads the device status word (after a sync)
 

@@ -199,6 +199,18 @@ def encode_random(dtype, seed, std, rows, cols, out=None):
     return out
 
 
+def noalloc_max_elements():
+    return int(lib().cmfc_noalloc_max_elements())
+
+
+def matmat_device_noalloc(model: Model, idx: int, d_x_ptr: int, b: int, d_y_ptr: int) -> bool:
+    """Quantized linear on caller-owned DEVICE buffers (raw pointers) for hosts that cannot allocate
+    device memory at call time; the tensor must already be resident and b * cols must fit the
+    library's fixed scratch (``noalloc_max_elements``).  No counterpart in the reference."""
+    check(lib().cmfc_matmat_device_noalloc(model.handle, idx, d_x_ptr, b, d_y_ptr))
+    return True
+
+
 def launch_count(reset=False):
     return int(lib().cmfc_launch_count(int(reset)))
 

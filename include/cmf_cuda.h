@@ -175,6 +175,26 @@ int cmfc_encode(int dtype, const float* w, size_t rows, size_t cols, uint8_t* pa
 /* same, generating w ~ N(0, std) on the device from `seed` (synthetic models for benchmarks) */
 int cmfc_encode_random(int dtype, uint64_t seed, float std, size_t rows, size_t cols, uint8_t* payload);
 
+/* ---- for callers that cannot allocate device memory ----
+ * No counterpart in the reference (its backends allocate freely); added for hosts where
+ * cudaMalloc is not an option at call time: code running inside another framework's memory pool,
+ * latency paths that cannot afford an allocation or the device-wide synchronization of a free, or
+ * deployments with a device-memory budget fixed at start-up.
+ *
+ * Y[b, rows] = X[b, cols] . W^T with DEVICE pointers: d_x f32 [b, cols] in, d_y f32 [b, rows]
+ * out, both owned by the caller.  The bf16 staging copy of X that the tensor-core kernel needs
+ * lives in a fixed 8 MiB array inside the library's device image, so b * cols must not exceed
+ * cmfc_noalloc_max_elements() (4 Mi); larger calls are rejected with CMFC_ERR_SHAPE.  The entry
+ * calls no cudaMalloc / cudaFree and no allocating library routine.  Preconditions: the thread
+ * has a device context (cmfc_set_device) and the tensor is already resident on it (any other
+ * entry uploads it; cmfc_weight_is_resident tells) -- otherwise CMFC_ERR_BAD_ARG /
+ * CMFC_ERR_NOT_FOUND.  The first call on a device looks up the array's device address; make that
+ * call before any stream capture.  All calls on a device share the array and it keeps the last
+ * call's contents; nothing in it needs clearing between calls, but two calls overlapping on the
+ * GPU would race, so serialize them.  Returns after the result is complete in d_y. */
+size_t cmfc_noalloc_max_elements(void);
+int cmfc_matmat_device_noalloc(cmfc_model* m, int64_t idx, const float* d_x, size_t b, float* d_y);
+
 /* ---- instrumentation ---- */
 /* kernels launched by this library on the current device since the last reset */
 uint64_t cmfc_launch_count(int reset);
