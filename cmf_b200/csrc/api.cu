@@ -84,7 +84,7 @@ extern "C" int cmfc_weight_is_resident(const cmfc_model* m, int64_t idx) {
 
 static int dequant_to(Context* c, DevWeight* w, float* d_out) {
     if (w->dtype == DT_Q8) launch_dequant_q8(reinterpret_cast<const int8_t*>(w->plane), w->scales, w->rows, w->cols, d_out, c->stream);
-    else if (w->is_q4()) launch_dequant_q4(w->plane, w->scales, w->rows, w->cols, d_out, c->stream);
+    else if (w->is_q4()) launch_dequant_q4(w->plane, w->scales, w->rows, w->cols, w->dtype == DT_Q4T ? 1 : 0, d_out, c->stream);
     else return fail(ERR_UNSUPPORTED, "dequant: not a quantized weight");
     c->launches++;
     return OK;
@@ -481,14 +481,24 @@ int upload_rope(Context* c, DevBuf* buf, const std::vector<int>& ids3, const int
 }
 void push_ids(std::vector<int>* v, int a, int b, int cc) { v->push_back(a); v->push_back(b); v->push_back(cc); }
 
+// `next` / `next_mods`: the block that follows on the SAME rows (or null); `xn_ready`: the previous
+// call already produced this block's input norm.
 int run_block(Context* c, cmfc_nextdit* d, const DitBlock& b, float* x, int n, const std::vector<int>& segs, const float* mods,
-              const DevBuf& rope, size_t rope_rows_n) {
+              const DevBuf& rope, size_t rope_rows_n, const DitBlock* next = nullptr, const float* next_mods = nullptr,
+              bool xn_ready = false) {
     BlockMod mod;
     if (b.modulated) {
         mod.s_msa = mods; mod.gate_msa = mods + d->hidden; mod.s_mlp = mods + 2 * d->hidden; mod.gate_mlp = mods + 3 * d->hidden;
     }
     const size_t half = rope_rows_n * (d->hd / 2);
-    return dev_block(c, b.bw, mod, x, n, segs, d->hidden, d->inter, d->nh, d->nkv, d->hd, d->eps, rope.as<double>(), rope.as<double>() + half);
+    BlockChain ch;
+    ch.xn_ready = xn_ready;
+    if (next) {
+        ch.next_norm1 = next->bw.norm1;
+        ch.next_s_msa = next->modulated ? next_mods : nullptr;
+    }
+    return dev_block(c, b.bw, mod, x, n, segs, d->hidden, d->inter, d->nh, d->nkv, d->hd, d->eps, rope.as<double>(),
+                     rope.as<double>() + half, &ch);
 }
 
 // y = W x + b for a small dense or q8 weight
@@ -531,7 +541,10 @@ int refine_caps(Context* c, cmfc_nextdit* d, const float* cap, const std::vector
     for (int s : segs)
         for (int i = 0; i < s; ++i) push_ids(&ids, i, 0, 0);
     CMFC_TRY(upload_rope(c, &d->rope_cap, ids, d->axes));
-    for (auto& b : d->ctx_ref) CMFC_TRY(run_block(c, d, b, out, rows, segs, nullptr, d->rope_cap, rows));
+    for (size_t l = 0; l < d->ctx_ref.size(); ++l) {
+        const DitBlock* nx = l + 1 < d->ctx_ref.size() ? &d->ctx_ref[l + 1] : nullptr;
+        CMFC_TRY(run_block(c, d, d->ctx_ref[l], out, rows, segs, nullptr, d->rope_cap, rows, nx, nullptr, l > 0));
+    }
     return OK;
 }
 
@@ -603,8 +616,11 @@ int forward_device(Context* c, cmfc_nextdit* d, const float* latents, int batch,
         d->rope_key = key.str();
     }
     size_t mk = 0;
-    for (auto& b : d->noise_ref)
-        CMFC_TRY(run_block(c, d, b, img.as<float>(), batch * n_img, segs_img, mods + (mk++) * 4 * hs, d->rope_img, (size_t)batch * n_img));
+    for (size_t l = 0; l < d->noise_ref.size(); ++l, ++mk) {
+        const DitBlock* nx = l + 1 < d->noise_ref.size() ? &d->noise_ref[l + 1] : nullptr;
+        CMFC_TRY(run_block(c, d, d->noise_ref[l], img.as<float>(), batch * n_img, segs_img, mods + mk * 4 * hs, d->rope_img,
+                           (size_t)batch * n_img, nx, mods + (mk + 1) * 4 * hs, l > 0));
+    }
     // ---- joint sequences: [cap | img] per (prompt, branch) ----
     CMFC_TRY(xb.ensure((size_t)n_joint * hs * 4));
     {
@@ -620,7 +636,10 @@ int forward_device(Context* c, cmfc_nextdit* d, const float* latents, int batch,
             }
     }
     for (size_t l = 0; l < d->layers.size(); ++l) {
-        CMFC_TRY(run_block(c, d, d->layers[l], xb.as<float>(), n_joint, segs_joint, mods + (mk++) * 4 * hs, d->rope_joint, (size_t)n_joint));
+        const DitBlock* nx = l + 1 < d->layers.size() ? &d->layers[l + 1] : nullptr;
+        CMFC_TRY(run_block(c, d, d->layers[l], xb.as<float>(), n_joint, segs_joint, mods + mk * 4 * hs, d->rope_joint, (size_t)n_joint,
+                           nx, mods + (mk + 1) * 4 * hs, l > 0));
+        ++mk;
         if (taps) CMFC_CUDA(cudaMemcpyAsync(taps + l * (size_t)n_joint * hs, xb.p, (size_t)n_joint * hs * 4, cudaMemcpyDeviceToDevice, s));
     }
     // ---- tail: LayerNorm * (1 + scale), project, unpatchify the image tokens ----

@@ -42,17 +42,46 @@ __device__ __forceinline__ float clampf(float v, float lo, float hi) { return fm
 
 // ---- payload -> planes ----
 
-// q4_tiled 18-byte tiles -> nibble plane [rows, cols/2] + transposed f32 scales [cols/32, rows]
+// Nibble order inside every 32-bit word of a GEMM nibble plane.  The container stores element e
+// of a word at nibble position e.  The plane stores elements (0,1,2,...,7) at positions
+// (0,4,1,5,2,6,3,7): then (w >> 4i) & 0x000f000f holds the ADJACENT elements 2i (low half) and
+// 2i+1 (high half), which is what a packed bf16x2 operand register needs.
+__host__ __device__ __forceinline__ uint32_t permute_nibbles(uint32_t w) {
+    uint32_t o = 0;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        const int pos = (e >> 1) + ((e & 1) << 2);
+        o |= ((w >> (4 * e)) & 0xFu) << (4 * pos);
+    }
+    return o;
+}
+__host__ __device__ __forceinline__ uint32_t plane_nibble(uint32_t word, int e) {
+    return (word >> (4 * ((e >> 1) + ((e & 1) << 2)))) & 0xFu;
+}
+
+// q4_tiled 18-byte tiles -> permuted nibble plane [rows, cols/2] + transposed group scales
+// [cols/32, rows].  The f16 scale s is stored as two bf16 halves of one 32-bit word:
+// hi = s truncated to 8 significant bits (low half), lo = s - hi (high half), both exact, so
+// fma.bf16x2(t, hi, t*lo) rounds the exact product t*s once.
 __global__ void q4t_split_kernel(const uint8_t* __restrict__ raw, int rows, int gpr, uint8_t* __restrict__ nib,
                                  float* __restrict__ scales_t) {
     const size_t g = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
     if (g >= (size_t)rows * gpr) return;
     const uint16_t* t = reinterpret_cast<const uint16_t*>(raw + g * 18);
     const int r = (int)(g / gpr), gi = (int)(g % gpr);
-    scales_t[(size_t)gi * rows + r] = half_bits_to_f32(t[0]);
-    uint16_t* dst = reinterpret_cast<uint16_t*>(nib + g * 16);
+    const float s = half_bits_to_f32(t[0]);
+    const uint32_t hi_bits = __float_as_uint(s) & 0xFFFF0000u;
+    const float lo = __fsub_rn(s, __uint_as_float(hi_bits));
+    const uint32_t packed = (hi_bits >> 16) | (__float_as_uint(lo) & 0xFFFF0000u);
+    reinterpret_cast<uint32_t*>(scales_t)[(size_t)gi * rows + r] = packed;
+    uint32_t* dst = reinterpret_cast<uint32_t*>(nib + g * 16);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) dst[k] = t[1 + k];
+    for (int k = 0; k < 4; ++k) dst[k] = permute_nibbles((uint32_t)t[1 + 2 * k] | ((uint32_t)t[2 + 2 * k] << 16));
+}
+
+__global__ void permute_plane_kernel(uint32_t* __restrict__ words, size_t n) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        words[i] = permute_nibbles(words[i]);
 }
 
 // q4tp 5-bit codes (LSB-first per row) + per-row ladders -> transposed f32 scales
@@ -80,15 +109,21 @@ __global__ void dequant_q8_kernel(const int8_t* __restrict__ q, const float* __r
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
         out[i] = __fmul_rn((float)q[i], row_scale[i / cols]);
 }
+// split_scales: 1 = q4t planes (bf16 hi/lo scale halves), 0 = q4tp planes (f32 ladder scales)
 __global__ void dequant_q4_kernel(const uint8_t* __restrict__ nib, const float* __restrict__ scales_t, int rows,
-                                  int cols, float* __restrict__ out) {
-    const size_t total = (size_t)rows * cols / 2;  // one byte -> two weights
+                                  int cols, int split_scales, float* __restrict__ out) {
+    const size_t total = (size_t)rows * cols / 8;  // one plane word -> eight weights
+    const uint32_t* words = reinterpret_cast<const uint32_t*>(nib);
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-        const size_t r = (2 * i) / cols, c = (2 * i) % cols;
-        const float s = scales_t[(c / 32) * rows + r];
-        const uint8_t b = nib[i];
-        out[2 * i] = __fmul_rn((float)(b & 0x0F) - 8.0f, s);
-        out[2 * i + 1] = __fmul_rn((float)(b >> 4) - 8.0f, s);
+        const size_t r = (8 * i) / cols, c = (8 * i) % cols;
+        float s = scales_t[(c / 32) * rows + r];
+        if (split_scales) {
+            const uint32_t u = __float_as_uint(s);
+            s = __fadd_rn(__uint_as_float(u << 16), __uint_as_float(u & 0xFFFF0000u));  // hi + lo, exact
+        }
+        const uint32_t w = words[i];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) out[8 * i + e] = __fmul_rn((float)plane_nibble(w, e) - 8.0f, s);
     }
 }
 
@@ -300,8 +335,12 @@ void launch_f16_to_f32(const uint16_t* h, float* out, int n, cudaStream_t s) {
 void launch_dequant_q8(const int8_t* q, const float* row_scale, int rows, int cols, float* out, cudaStream_t s) {
     dequant_q8_kernel<<<capped((size_t)rows * cols, 256), 256, 0, s>>>(q, row_scale, rows, cols, out);
 }
-void launch_dequant_q4(const uint8_t* nib, const float* scales_t, int rows, int cols, float* out, cudaStream_t s) {
-    dequant_q4_kernel<<<capped((size_t)rows * cols / 2, 256), 256, 0, s>>>(nib, scales_t, rows, cols, out);
+void launch_dequant_q4(const uint8_t* nib, const float* scales_t, int rows, int cols, int split_scales, float* out,
+                       cudaStream_t s) {
+    dequant_q4_kernel<<<capped((size_t)rows * cols / 8, 256), 256, 0, s>>>(nib, scales_t, rows, cols, split_scales, out);
+}
+void launch_permute_plane(uint8_t* nib, size_t bytes, cudaStream_t s) {
+    permute_plane_kernel<<<capped(bytes / 4, 256), 256, 0, s>>>(reinterpret_cast<uint32_t*>(nib), bytes / 4);
 }
 void launch_encode_q8_row(const float* w, int rows, int cols, uint8_t* payload, cudaStream_t s) {
     encode_q8_row_kernel<<<rows, 256, 0, s>>>(w, rows, cols, payload);

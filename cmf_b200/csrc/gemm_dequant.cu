@@ -84,19 +84,37 @@ struct Q4Scales {
         : s0(s), s4(s * 0.0625f), s8(s * 0.00390625f), s12(s * 0.000244140625f), s16(s * 1.52587890625e-05f) {}
 };
 
+// One plane word (elements 0..7 at nibble positions 0,4,1,5,2,6,3,7) -> four bf16x2 registers.
+// f32 route, any f32 scale (q4tp ladder scales): exact product, one rounding to bf16.
 __device__ __forceinline__ void unpack_q4_word(uint32_t w, const Q4Scales& sc, uint32_t* o) {
-    uint32_t hi = w >> 12;
-    o[0] = pack_bf16(nib_times<0>(w, sc.s0), nib_times<4>(w, sc.s4));
-    o[1] = pack_bf16(nib_times<8>(w, sc.s8), nib_times<12>(w, sc.s12));
-    o[2] = pack_bf16(nib_times<16>(w, sc.s16), nib_times<8>(hi, sc.s8));
-    o[3] = pack_bf16(nib_times<12>(hi, sc.s12), nib_times<16>(hi, sc.s16));
+    uint32_t hi = w >> 12;  // positions 4..7 -> bits 4, 8, 12, 16
+    o[0] = pack_bf16(nib_times<0>(w, sc.s0), nib_times<4>(hi, sc.s4));
+    o[1] = pack_bf16(nib_times<4>(w, sc.s4), nib_times<8>(hi, sc.s8));
+    o[2] = pack_bf16(nib_times<8>(w, sc.s8), nib_times<12>(hi, sc.s12));
+    o[3] = pack_bf16(nib_times<12>(w, sc.s12), nib_times<16>(hi, sc.s16));
+}
+
+// bf16x2 route for q4_tiled, whose scale is an f16 value s = hi + lo with hi (8 significant bits)
+// and lo (3 bits) both exact bf16: t = nib - 8 is exact, t*lo is exact (at most 7 bits), and
+// fma.rn(t, hi, t*lo) rounds the exact product t*s once -- the same bits as the f32 route.
+__device__ __forceinline__ void unpack_q4t_word(uint32_t w, uint32_t hi2, uint32_t lo2, uint32_t* o) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t m = ((w >> (4 * i)) & 0x000f000fu) | 0x43004300u;  // bf16 128 + nib, twice
+        uint32_t t, c;
+        asm("sub.bf16x2 %0, %1, %2;" : "=r"(t) : "r"(m), "r"(0x43084308u));  // - 136
+        asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(c) : "r"(t), "r"(lo2));
+        asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(o[i]) : "r"(t), "r"(hi2), "r"(c));
+    }
 }
 
 __device__ __forceinline__ uint4 lds128(const uint8_t* p) { return *reinterpret_cast<const uint4*>(p); }
 
 __device__ __forceinline__ float silu_f(float v) { return __fdividef(v, 1.0f + __expf(-v)); }
 
-template <int WKIND>  // 0 = q8 (int8 plane), 1 = q4 (nibble plane + transposed f32 scales)
+// WKIND: 0 = q8 (int8 plane); 1 = q4tp (nibble plane + transposed f32 scales);
+//        2 = q4_tiled (nibble plane + transposed scales split into bf16 hi/lo halves)
+template <int WKIND>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_dequant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
                     const __grid_constant__ CUtensorMap tm_s, GemmParams p) {
@@ -117,7 +135,7 @@ gemm_dequant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
     const int tiles_n = p.N / TW;
     const int tiles = tiles_m * tiles_n;
     constexpr uint32_t W_BYTES = (WKIND == 0) ? TW * BK : TW * BK / 2;
-    constexpr uint32_t TX_BYTES = X_STAGE + W_BYTES + (WKIND == 1 ? S_STAGE : 0);
+    constexpr uint32_t TX_BYTES = X_STAGE + W_BYTES + (WKIND != 0 ? S_STAGE : 0);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -136,7 +154,7 @@ gemm_dequant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         mbar_fence_init();
         tma_prefetch_desc(&tm_x);
         tma_prefetch_desc(&tm_w);
-        if (WKIND == 1) tma_prefetch_desc(&tm_s);
+        if (WKIND != 0) tma_prefetch_desc(&tm_s);
     }
     if (warp == 1) {
         tmem_alloc(&bars->tmem_base, TMEM_COLS);
@@ -238,12 +256,21 @@ gemm_dequant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
                     const uint8_t* wrow = w_smem + s * W_STAGE + row * 32;
                     const int sw = (row >> 2) & 1;  // 32-byte swizzle: chunk ^= address bit 7
                     uint4 v = lds128(wrow + ((half ^ sw) << 4));
-                    const float sc = reinterpret_cast<const float*>(s_smem + s * S_STAGE)[half * TW + row];
-                    const Q4Scales q(sc);
-                    unpack_q4_word(v.x, q, a + 0);
-                    unpack_q4_word(v.y, q, a + 4);
-                    unpack_q4_word(v.z, q, a + 8);
-                    unpack_q4_word(v.w, q, a + 12);
+                    if (WKIND == 1) {
+                        const float sc = reinterpret_cast<const float*>(s_smem + s * S_STAGE)[half * TW + row];
+                        const Q4Scales q(sc);
+                        unpack_q4_word(v.x, q, a + 0);
+                        unpack_q4_word(v.y, q, a + 4);
+                        unpack_q4_word(v.z, q, a + 8);
+                        unpack_q4_word(v.w, q, a + 12);
+                    } else {
+                        const uint32_t sc = reinterpret_cast<const uint32_t*>(s_smem + s * S_STAGE)[half * TW + row];
+                        const uint32_t hi2 = __byte_perm(sc, sc, 0x1010), lo2 = __byte_perm(sc, sc, 0x3232);
+                        unpack_q4t_word(v.x, hi2, lo2, a + 0);
+                        unpack_q4t_word(v.y, hi2, lo2, a + 4);
+                        unpack_q4t_word(v.z, hi2, lo2, a + 8);
+                        unpack_q4t_word(v.w, hi2, lo2, a + 12);
+                    }
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bars->empty[s]);  // the packed bytes are in registers
@@ -297,7 +324,8 @@ gemm_dequant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
                     const bool odd = lane & 1;
 #pragma unroll
                     for (int j = 0; j < 32; j += 2) {
-                        float mine_a = __uint_as_float(v[j]) * rs, mine_b = __uint_as_float(v[j + 1]) * rs;
+                        float mine_a = __uint_as_float(v[j]), mine_b = __uint_as_float(v[j + 1]);
+                        if (WKIND == 0) { mine_a *= rs; mine_b *= rs; }
                         float got = __shfl_xor_sync(0xffffffffu, odd ? mine_a : mine_b, 1);
                         float g = odd ? got : mine_a;
                         float u = odd ? mine_b : got;
@@ -330,8 +358,8 @@ int launch_gemm_dequant(int wkind, const CUtensorMap& tm_x, const CUtensorMap& t
                         const GemmParams& p, int num_sms, cudaStream_t stream) {
     if (p.K % BK != 0 || p.N % TW != 0 || p.M <= 0)
         return fail(ERR_SHAPE, "dequant GEMM needs K % 64 == 0 and N % 128 == 0");
-    static bool configured[2] = {false, false};
-    auto kern = wkind == 0 ? gemm_dequant_kernel<0> : gemm_dequant_kernel<1>;
+    static bool configured[3] = {false, false, false};
+    auto kern = wkind == 0 ? gemm_dequant_kernel<0> : (wkind == 1 ? gemm_dequant_kernel<1> : gemm_dequant_kernel<2>);
     if (!configured[wkind]) {
         CMFC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         configured[wkind] = true;

@@ -48,7 +48,10 @@ void launch_q4tp_scales(const uint8_t* codes, int code_stride, const float* ladd
 void launch_f16_to_f32(const uint16_t* h, float* out, int n, cudaStream_t s);
 // planes -> exact f32 weights [rows, cols] (the bit-exactness check)
 void launch_dequant_q8(const int8_t* q, const float* row_scale, int rows, int cols, float* out, cudaStream_t s);
-void launch_dequant_q4(const uint8_t* nib, const float* scales_t, int rows, int cols, float* out, cudaStream_t s);
+void launch_dequant_q4(const uint8_t* nib, const float* scales_t, int rows, int cols, int split_scales, float* out,
+                       cudaStream_t s);
+// in place: container nibble order -> GEMM plane order (see permute_nibbles in codec_kernels.cu)
+void launch_permute_plane(uint8_t* nib, size_t bytes, cudaStream_t s);
 // device-side encoders (bit-exact with the reference quantizer; transcendental values come
 // from host-built lookup tables indexed by f16 bit pattern)
 void launch_encode_q8_row(const float* w, int rows, int cols, uint8_t* payload, cudaStream_t s);

@@ -418,7 +418,8 @@ int get_weight(Context* c, Model* m, int64_t idx, DevWeight** out) {
         CMFC_CUDA(cudaMemcpyAsync(d_codes, params + (size_t)rows * 4, codes_b, cudaMemcpyHostToDevice, s));
         CMFC_CUDA(cudaMemcpyAsync(d_lad, lad.data(), lad_b, cudaMemcpyHostToDevice, s));
         launch_q4tp_scales(d_codes, stride, d_lad, rows, gpr, w->scales, s);
-        c->launches++;
+        launch_permute_plane(w->plane, nib_b, s);
+        c->launches += 2;
         CMFC_CUDA(cudaStreamSynchronize(s));
     }
     CMFC_CUDA(cudaGetLastError());
@@ -470,12 +471,13 @@ int get_weight_concat(Context* c, Model* m, int64_t a, int64_t b, int64_t cc, De
     const bool q4 = parts[0]->is_q4();
     int rows = 0;
     for (auto* p : parts) {
-        if (p->cols != parts[0]->cols || p->is_q4() != q4 || (!q4 && p->dtype != DT_Q8))
-            return fail(ERR_UNSUPPORTED, "fused projection needs one codec family and one input width");
+        // q4t and q4tp keep different scale formats on the device, so a fused view needs one codec
+        if (p->cols != parts[0]->cols || p->dtype != parts[0]->dtype)
+            return fail(ERR_UNSUPPORTED, "fused projection needs one codec and one input width");
         rows += p->rows;
     }
     std::unique_ptr<DevWeight> w(new DevWeight());
-    w->dtype = q4 ? DT_Q4T : DT_Q8;  // q4t and q4tp share planes once uploaded
+    w->dtype = parts[0]->dtype;
     w->rows = rows; w->cols = parts[0]->cols;
     CMFC_TRY(alloc_planes(w.get()));
     const size_t row_b = q4 ? w->cols / 2 : w->cols;
@@ -505,11 +507,11 @@ int get_weight_interleaved(Context* c, Model* m, int64_t a, int64_t b, DevWeight
     DevWeight *pa = nullptr, *pb = nullptr;
     CMFC_TRY(get_weight(c, m, a, &pa));
     CMFC_TRY(get_weight(c, m, b, &pb));
-    if (pa->rows != pb->rows || pa->cols != pb->cols || pa->is_q4() != pb->is_q4())
-        return fail(ERR_UNSUPPORTED, "SwiGLU gate and up projections must share shape and codec family");
+    if (pa->rows != pb->rows || pa->cols != pb->cols || pa->dtype != pb->dtype)
+        return fail(ERR_UNSUPPORTED, "SwiGLU gate and up projections must share shape and codec");
     const bool q4 = pa->is_q4();
     std::unique_ptr<DevWeight> w(new DevWeight());
-    w->dtype = q4 ? DT_Q4T : DT_Q8;
+    w->dtype = pa->dtype;
     w->rows = 2 * pa->rows; w->cols = pa->cols;
     CMFC_TRY(alloc_planes(w.get()));
     const size_t row_b = q4 ? w->cols / 2 : w->cols;
@@ -542,7 +544,7 @@ int dev_gemm(Context* c, DevWeight* w, const __nv_bfloat16* x, int M, void* out,
     p.row_scale = w->dtype == DT_Q8 ? w->scales : nullptr;
     p.status = c->status;
     c->launches++;
-    return launch_gemm_dequant(w->dtype == DT_Q8 ? 0 : 1, tm_x, w->tm_w, w->tm_s, p, c->num_sms, c->stream);
+    return launch_gemm_dequant(w->dtype == DT_Q8 ? 0 : (w->dtype == DT_Q4TP ? 1 : 2), tm_x, w->tm_w, w->tm_s, p, c->num_sms, c->stream);
 }
 
 // Segment table on the device: [nseg+1] token offsets, then [nseg] first V^T column of each
@@ -593,7 +595,8 @@ int dev_attention(Context* c, const __nv_bfloat16* q, const __nv_bfloat16* k, co
 }
 
 int dev_block(Context* c, const BlockWeights& bw, const BlockMod& mod, float* x, int n, const std::vector<int>& segs,
-              int hidden, int inter, int nh, int nkv, int hd, double eps, const double* cos_t, const double* sin_t) {
+              int hidden, int inter, int nh, int nkv, int hd, double eps, const double* cos_t, const double* sin_t,
+              const BlockChain* chain) {
     cudaStream_t s = c->stream;
     const int qkv_w = (nh + 2 * nkv) * hd;
     SegTable st;
@@ -614,7 +617,7 @@ int dev_block(Context* c, const BlockWeights& bw, const BlockMod& mod, float* x,
     CMFC_TRY(att.ensure((size_t)n * nh * hd * 2));
     CMFC_TRY(proj.ensure((size_t)n * hidden * 4));
     CMFC_TRY(act.ensure((size_t)n * inter * 2));
-    {
+    if (!(chain && chain->xn_ready)) {
         SpanGuard g(c, "mod-norm");
         launch_rms_mod(x, bw.norm1, mod.s_msa, eps, n, hidden, xn.as<__nv_bfloat16>(), nullptr, s);
         c->launches++;
@@ -652,7 +655,11 @@ int dev_block(Context* c, const BlockWeights& bw, const BlockMod& mod, float* x,
     }
     {
         SpanGuard g(c, "mod-norm");
-        launch_gated_residual(x, proj.as<float>(), bw.ffn_norm2, mod.gate_mlp, eps, n, hidden, s);
+        if (chain && chain->next_norm1)
+            launch_residual_then_norm(x, proj.as<float>(), bw.ffn_norm2, mod.gate_mlp, chain->next_norm1, chain->next_s_msa, eps,
+                                      n, hidden, xn.as<__nv_bfloat16>(), s);
+        else
+            launch_gated_residual(x, proj.as<float>(), bw.ffn_norm2, mod.gate_mlp, eps, n, hidden, s);
         c->launches++;
     }
     CMFC_CUDA(cudaGetLastError());

@@ -116,8 +116,17 @@ struct BlockMod {  // all null for an unmodulated block; gates already tanh'd
     const float *s_msa = nullptr, *gate_msa = nullptr, *s_mlp = nullptr, *gate_mlp = nullptr;
 };
 // One block over x [n, hidden] f32 in place (crates/cortiq-engine/src/dit.rs:943-1177).
+// Chaining: when `next` is given, the block's last pass also writes the NEXT block's modulated
+// input norm (bf16) so that block can skip its own first pass (`xn_ready`); this saves one read
+// of x per block.
+struct BlockChain {
+    bool xn_ready = false;            // the shared bf16 norm buffer already holds this block's input norm
+    const float* next_norm1 = nullptr;  // next block's norm1 weight, or null
+    const float* next_s_msa = nullptr;  // next block's s_msa (null for an unmodulated block)
+};
 int dev_block(Context* c, const BlockWeights& bw, const BlockMod& mod, float* x, int n, const std::vector<int>& segs,
-              int hidden, int inter, int nh, int nkv, int hd, double eps, const double* cos_t, const double* sin_t);
+              int hidden, int inter, int nh, int nkv, int hd, double eps, const double* cos_t, const double* sin_t,
+              const BlockChain* chain = nullptr);
 
 bool row_cols_supported(int cols);
 void launch_gemv_silu2(const GemvParams& p, float* y_silu, cudaStream_t s);

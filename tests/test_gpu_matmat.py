@@ -65,6 +65,26 @@ def test_matmat_sweep_shapes_sampled(tmp_path, dt):
         assert np.isfinite(got).all()
 
 
+@pytest.mark.parametrize("dt", [oc.Q8_ROW, oc.Q4_TILED, oc.Q4TP])
+def test_gemm_operand_is_the_rounded_reference_dequant(tmp_path, dt):
+    """One-hot activations read the tensor-core A operand back: Y[k, n] = operand[n, k].  For the
+    4-bit codecs it must be RN_bf16(reference f32 dequant) bit for bit; for q8 the integer level
+    is the operand and the f32 row scale is applied after, which reproduces the dequant exactly."""
+    from cmf_b200 import Model, gpu
+    rows, cols = 256, 256
+    rng = np.random.default_rng(77)
+    w = (rng.standard_normal((rows, cols)) * np.exp(rng.uniform(-6, 3, (rows, 1)))).astype(np.float32)
+    w[5, 40] = 900.0
+    path = str(tmp_path / "w.cmf")
+    q = single_weight_file(path, [("w", dt, w)])["w"]
+    x = np.eye(cols, dtype=np.float32)
+    with Model(path) as m:
+        got = _call(gpu, dt, m, m.index("w"), x, rows, cols)   # [cols, rows]
+    dense = oc.dequant(dt, q.payload, rows, cols)
+    want = dense.T if dt == oc.Q8_ROW else oc.bf16_round(dense).T
+    assert np.array_equal(got.view(np.uint32), np.ascontiguousarray(want).view(np.uint32))
+
+
 def test_matmat_rejects_wrong_codec_and_shape(tmp_path):
     from cmf_b200 import CmfCudaError, Model, gpu
     rng = np.random.default_rng(0)
