@@ -14,10 +14,6 @@ namespace cmfc {
 const std::string& last_error();
 }
 
-struct cmfc_model {
-    Model* m;
-};
-
 #define NEED_CTX()                                                         \
     Context* c = ctx();                                                    \
     if (!c) return last_error().empty() ? fail(ERR_CUDA, "no CUDA device") : ERR_CUDA;

@@ -12,10 +12,6 @@
 
 using namespace cmfc;
 
-struct cmfc_model {
-    Model* m;
-};
-
 namespace {
 
 // 8 MiB of bf16 activations: b * cols <= 4 Mi elements (e.g. 1820 tokens of width 2304).  Every

@@ -139,3 +139,8 @@ struct SpanGuard {
 };
 
 }  // namespace cmfc
+
+// The opaque handle of the C ABI wraps the container.
+struct cmfc_model {
+    cmfc::Model* m;
+};
