@@ -341,6 +341,13 @@ struct cmfc_nextdit {
     float gs = 4.0f;
     bool cfg = false;
     std::vector<double> sig;
+    uint32_t next_step = 0;            // value of the device step counter
+    // one captured denoise step (all launches of forward + CFG/Euler), replayed by later steps
+    cudaGraphExec_t graph = nullptr;
+    uint64_t graph_epoch = 0;          // allocation epoch at capture time
+    uint64_t graph_launches = 0;       // kernel launches inside the graph
+    std::string graph_key;
+    int eager_steps = 0;               // steps run eagerly since the last begin (the first one warms buffers)
 };
 
 namespace {
@@ -544,6 +551,18 @@ int refine_caps(Context* c, cmfc_nextdit* d, const float* cap, const std::vector
     return OK;
 }
 
+// Upload (t_i, d_i) pairs and reset the device step counter.  The pinned staging area is reused,
+// so wait for earlier work on the stream that may still read it.
+int upload_schedule(Context* c, const std::vector<float>& td, int start_step) {
+    if (td.size() > 2 * (size_t)Context::MAX_STEPS) return fail(ERR_BAD_ARG, "too many steps (limit 1024)");
+    CMFC_CUDA(cudaStreamSynchronize(c->stream));
+    memcpy(c->sched_host, td.data(), td.size() * 4);
+    reinterpret_cast<int*>(c->sched_host)[2 * Context::MAX_STEPS] = start_step;
+    CMFC_CUDA(cudaMemcpyAsync(c->sched, c->sched_host, td.size() * 4, cudaMemcpyHostToDevice, c->stream));
+    CMFC_CUDA(cudaMemcpyAsync(c->step_counter, c->sched_host + 2 * Context::MAX_STEPS, 4, cudaMemcpyHostToDevice, c->stream));
+    return OK;
+}
+
 // One velocity prediction for `batch` prompts.  caps[q] (device, refined) for q in [0, nseq):
 // nseq = 1 (no CFG) or 2 (cond, uncond); each is [batch, cap_ns[q], hidden].  preds[q] receive
 // [batch, c, h, w].  taps (optional, device): x after each joint layer.
@@ -565,7 +584,7 @@ int forward_device(Context* c, cmfc_nextdit* d, const float* latents, int batch,
     float* mods = out_scale + hs;
     {
         SpanGuard g(c, "head-tail");
-        launch_time_freqs(t, freqs, s);
+        launch_time_freqs(c->sched, c->step_counter, freqs, s);
         c->launches++;
         gemv_dense(c, d->t1w, d->temb, 256, d->t1b, freqs, temb /*scratch*/, h1_silu);
         gemv_dense(c, d->t2w, d->temb, d->temb, d->t2b, h1_silu, temb, temb_silu);
@@ -776,6 +795,7 @@ static int forward_host(cmfc_nextdit* d, const float* latent, size_t h, size_t w
     const float* caps[2] = {cc.as<float>(), cu.as<float>()};
     const int cap_ns[2] = {(int)cap_c_n, (int)cap_u_n};
     float* preds[2] = {pc.as<float>(), pu.as<float>()};
+    CMFC_TRY(upload_schedule(c, {t, 0.0f}, 0));
     CMFC_TRY(forward_device(c, d, lat.as<float>(), 1, (int)h, (int)w, nseq, caps, cap_ns, t, preds, taps ? tp.as<float>() : nullptr));
     CMFC_CUDA(cudaMemcpyAsync(pred_c, pc.p, lat_n * 4, cudaMemcpyDeviceToHost, c->stream));
     if (nseq > 1) CMFC_CUDA(cudaMemcpyAsync(pred_u, pu.p, lat_n * 4, cudaMemcpyDeviceToHost, c->stream));
@@ -831,23 +851,89 @@ extern "C" int cmfc_denoise_begin(cmfc_nextdit* d, const float* latents, size_t 
         CMFC_CUDA(cudaMemcpyAsync(raw_u, cap_u, batch * cap_u_n * cf * 4, cudaMemcpyHostToDevice, c->stream));
         CMFC_TRY(refine_caps(c, d, raw_u, std::vector<int>(batch, (int)cap_u_n), d->cap_u_r.as<float>()));
     }
+    // timesteps t_i = 1 - sigma_i and step sizes d_i = sigma_{i+1} - sigma_i live on the device
+    std::vector<float> td(2 * steps);
+    for (uint32_t i = 0; i < steps; ++i) {
+        td[2 * i] = (float)(1.0 - d->sig[i]);
+        td[2 * i + 1] = (float)(d->sig[i + 1] - d->sig[i]);
+    }
+    CMFC_TRY(upload_schedule(c, td, 0));
+    d->next_step = 0;
+    d->eager_steps = 0;
+    std::ostringstream key;
+    key << batch << ":" << h << ":" << w << ":" << cap_n << ":" << d->cap_u_n << ":" << guidance_scale;
+    if (d->graph && key.str() != d->graph_key) {
+        cudaGraphExecDestroy(d->graph);
+        d->graph = nullptr;
+    }
+    d->graph_key = key.str();
     return OK;
 }
+
+namespace {
+// every launch of one denoise step, in stream order
+int enqueue_step(Context* c, cmfc_nextdit* d) {
+    const float* caps[2] = {d->cap_c_r.as<float>(), d->cap_u_r.as<float>()};
+    const int cap_ns[2] = {(int)d->cap_n, (int)d->cap_u_n};
+    float* preds[2] = {d->pred_c.as<float>(), d->pred_u.as<float>()};
+    CMFC_TRY(forward_device(c, d, d->latents.as<float>(), (int)d->batch, (int)d->lh, (int)d->lw, d->cfg ? 2 : 1, caps, cap_ns, 0.0f, preds, nullptr));
+    launch_cfg_euler(d->latents.as<float>(), d->pred_c.as<float>(), d->pred_u.as<float>(), d->gs, c->sched, c->step_counter,
+                     (int)(d->batch * d->ch * d->lh), (int)d->lw, d->cfg ? 1 : 0, c->stream);
+    launch_advance_step(c->step_counter, c->stream);
+    c->launches += 2;
+    CMFC_CUDA(cudaGetLastError());
+    return OK;
+}
+}  // namespace
 
 extern "C" int cmfc_denoise_step(cmfc_nextdit* d, uint32_t i) {
     NEED(d && d->batch > 0 && i < d->steps, "denoise_step: no loop in progress or step out of range");
     NEED_CTX();
-    const float t = (float)(1.0 - d->sig[i]);
-    const float* caps[2] = {d->cap_c_r.as<float>(), d->cap_u_r.as<float>()};
-    const int cap_ns[2] = {(int)d->cap_n, (int)d->cap_u_n};
-    float* preds[2] = {d->pred_c.as<float>(), d->pred_u.as<float>()};
-    CMFC_TRY(forward_device(c, d, d->latents.as<float>(), (int)d->batch, (int)d->lh, (int)d->lw, d->cfg ? 2 : 1, caps, cap_ns, t, preds, nullptr));
-    const float dd = (float)(d->sig[i + 1] - d->sig[i]);
-    launch_cfg_euler(d->latents.as<float>(), d->pred_c.as<float>(), d->pred_u.as<float>(), d->gs, dd,
-                     (int)(d->batch * d->ch * d->lh), (int)d->lw, d->cfg ? 1 : 0, c->stream);
-    c->launches++;
-    CMFC_CUDA(cudaGetLastError());
-    return OK;
+    if (i != d->next_step) {  // out-of-order step: move the device counter
+        CMFC_CUDA(cudaStreamSynchronize(c->stream));
+        reinterpret_cast<int*>(c->sched_host)[2 * Context::MAX_STEPS] = (int)i;
+        CMFC_CUDA(cudaMemcpyAsync(c->step_counter, c->sched_host + 2 * Context::MAX_STEPS, 4, cudaMemcpyHostToDevice, c->stream));
+    }
+    d->next_step = i + 1;
+    // The step's ~320 launches are captured once into a CUDA graph and replayed: the timestep and
+    // step size come from the device-resident schedule, so nothing in the graph depends on i.  The
+    // first step after begin runs eagerly (it may grow workspaces and upload tables); profiling
+    // spans need eager launches too.
+    static const bool graphs_on = !(getenv("CMFC_GRAPH") && atoi(getenv("CMFC_GRAPH")) == 0);
+    if (d->graph && d->graph_epoch != alloc_epoch()) {
+        cudaGraphExecDestroy(d->graph);
+        d->graph = nullptr;
+    }
+    if (graphs_on && !c->prof.on && d->graph) {
+        CMFC_CUDA(cudaGraphLaunch(d->graph, c->stream));
+        c->launches += d->graph_launches;
+        return OK;
+    }
+    if (graphs_on && !c->prof.on && d->eager_steps >= 1) {
+        const uint64_t before = c->launches, epoch = alloc_epoch();
+        cudaGraph_t g = nullptr;
+        CMFC_CUDA(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
+        const int rc = enqueue_step(c, d);
+        const cudaError_t ce = cudaStreamEndCapture(c->stream, &g);
+        if (rc == OK && ce == cudaSuccess && g && epoch == alloc_epoch() &&
+            cudaGraphInstantiate(&d->graph, g, 0) == cudaSuccess) {
+            d->graph_launches = c->launches - before;
+            c->launches = before;
+            d->graph_epoch = epoch;
+            cudaGraphDestroy(g);
+            CMFC_CUDA(cudaGraphLaunch(d->graph, c->stream));
+            c->launches += d->graph_launches;
+            return OK;
+        }
+        // capture did not work out (e.g. a workspace had to grow): nothing ran; fall through to eager
+        if (g) cudaGraphDestroy(g);
+        d->graph = nullptr;
+        c->launches = before;
+        cudaGetLastError();
+        if (rc != OK) return rc;
+    }
+    d->eager_steps++;
+    return enqueue_step(c, d);
 }
 
 extern "C" int cmfc_denoise_end(cmfc_nextdit* d, float* latents) {

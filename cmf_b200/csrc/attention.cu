@@ -301,8 +301,14 @@ int attn_smem_bytes(int hd) {
 template <int HD>
 static int launch_hd(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_vt, const AttnParams& p,
                      cudaStream_t stream) {
-    CMFC_CUDA(cudaFuncSetAttribute(attention_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   AttnSmem<HD>::TOTAL));
+    static bool configured[64] = {false};  // per instantiation and device; never repeated inside a stream capture
+    int dev = 0;
+    CMFC_CUDA(cudaGetDevice(&dev));
+    if (!configured[dev & 63]) {
+        CMFC_CUDA(cudaFuncSetAttribute(attention_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       AttnSmem<HD>::TOTAL));
+        configured[dev & 63] = true;
+    }
     dim3 grid((p.max_seg + 2 * QT - 1) / (2 * QT), p.nh, p.nseg);
     attention_kernel<HD><<<grid, ATTN_THREADS, AttnSmem<HD>::TOTAL, stream>>>(tm_q, tm_k, tm_vt, p);
     CMFC_CUDA(cudaGetLastError());

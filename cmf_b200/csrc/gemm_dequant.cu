@@ -358,11 +358,13 @@ int launch_gemm_dequant(int wkind, const CUtensorMap& tm_x, const CUtensorMap& t
                         const GemmParams& p, int num_sms, cudaStream_t stream) {
     if (p.K % BK != 0 || p.N % TW != 0 || p.M <= 0)
         return fail(ERR_SHAPE, "dequant GEMM needs K % 64 == 0 and N % 128 == 0");
-    static bool configured[3] = {false, false, false};
+    static bool configured[3][64] = {};  // per codec kernel and device
     auto kern = wkind == 0 ? gemm_dequant_kernel<0> : (wkind == 1 ? gemm_dequant_kernel<1> : gemm_dequant_kernel<2>);
-    if (!configured[wkind]) {
+    int dev = 0;
+    CMFC_CUDA(cudaGetDevice(&dev));
+    if (!configured[wkind][dev & 63]) {
         CMFC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        configured[wkind] = true;
+        configured[wkind][dev & 63] = true;
     }
     const int tiles = ((p.M + TT - 1) / TT) * (p.N / TW);
     const int grid = tiles < num_sms ? tiles : num_sms;

@@ -88,15 +88,17 @@ void launch_gemv(const GemvParams& p, cudaStream_t s);
 // small exact-f32 GEMM: Y[M,N] = A[M,K] . W[N,K]^T + b
 void launch_sgemm_nt_bias(const float* a, const float* w, const float* bias, float* y, int M, int N, int K,
                           cudaStream_t s);
-void launch_time_freqs(float t, float* out256, cudaStream_t s);
+void launch_time_freqs(const float* sched, const int* counter, float* out256, cudaStream_t s);
+void launch_advance_step(int* counter, cudaStream_t s);
 void launch_patchify(const float* latent, int c, int h, int w, int p, float* tok, cudaStream_t s);
 void launch_unpatchify(const float* tok, int c, int h, int w, int p, float* latent, cudaStream_t s);
 // LayerNorm without affine (eps 1e-6), times (1 + scale), f32 out
 void launch_layernorm_scale(const float* x, const float* scale, int rows, int cols, float* out, cudaStream_t s);
 void launch_silu_mul(const __nv_bfloat16* gu, int rows, int inter, __nv_bfloat16* out, cudaStream_t s);
 // CFG combine with per-row norm rescale, then Euler update: x -= d * pred
-void launch_cfg_euler(float* latents, const float* cond, const float* uncond, float gs, float d, int rows, int lw,
-                      int use_cfg, cudaStream_t s);
+// schedule: sched[2*i] = timestep t_i, sched[2*i+1] = sigma_{i+1} - sigma_i; *counter = current step
+void launch_cfg_euler(float* latents, const float* cond, const float* uncond, float gs, const float* sched,
+                      const int* counter, int rows, int lw, int use_cfg, cudaStream_t s);
 void launch_transpose_head_major(const float* src_head_major, int heads, int n, int hd, float scale,
                                  __nv_bfloat16* dst_token_major, cudaStream_t s);
 void launch_v_head_major_to_vt(const float* v_head_major, int nkv, int n, int hd, __nv_bfloat16* vt, int vt_pitch,

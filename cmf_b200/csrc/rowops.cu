@@ -317,7 +317,10 @@ sgemm_nt_kernel(const float* __restrict__ a, const float* __restrict__ w, const 
 }
 
 // sinusoidal timestep features, cos first (dit.rs:592-600): f64 angle, f32 result
-__global__ void time_freqs_kernel(float t, float* out) {
+// The timestep comes from the device-resident schedule (t at sched[2*step], sigma step at
+// sched[2*step+1], step = *counter), so the same launch sequence can be replayed as a CUDA graph.
+__global__ void time_freqs_kernel(const float* __restrict__ sched, const int* __restrict__ counter, float* out) {
+    const float t = sched[2 * *counter];
     const int i = threadIdx.x;  // 128 threads
     const double ang = (double)t * exp(-log(10000.0) * (double)i / 128.0);
     out[i] = (float)cos(ang);
@@ -372,7 +375,8 @@ __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, int rows, 
 // CFG combine + per-row norm rescale + Euler update (imagegen.rs:186-213); one warp per row of lw
 __global__ void __launch_bounds__(256)
 cfg_euler_kernel(float* __restrict__ latents, const float* __restrict__ cond, const float* __restrict__ uncond,
-                 float gs, float d, int rows, int lw, int use_cfg) {
+                 float gs, const float* __restrict__ sched, const int* __restrict__ counter, int rows, int lw, int use_cfg) {
+    const float d = sched[2 * *counter + 1];
     const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (row >= rows) return;
@@ -517,7 +521,11 @@ void launch_sgemm_nt_bias(const float* a, const float* w, const float* bias, flo
     dim3 g((N + 63) / 64, (M + 63) / 64);
     sgemm_nt_kernel<<<g, 256, 0, s>>>(a, w, bias, y, M, N, K);
 }
-void launch_time_freqs(float t, float* out256, cudaStream_t s) { time_freqs_kernel<<<1, 128, 0, s>>>(t, out256); }
+__global__ void advance_step_kernel(int* counter) { *counter += 1; }
+void launch_time_freqs(const float* sched, const int* counter, float* out256, cudaStream_t s) {
+    time_freqs_kernel<<<1, 128, 0, s>>>(sched, counter, out256);
+}
+void launch_advance_step(int* counter, cudaStream_t s) { advance_step_kernel<<<1, 1, 0, s>>>(counter); }
 void launch_patchify(const float* latent, int c, int h, int w, int p, float* tok, cudaStream_t s) {
     patchify_kernel<<<grid_for((size_t)c * h * w, 256), 256, 0, s>>>(latent, c, h, w, p, tok, 0, nullptr);
 }
@@ -528,9 +536,9 @@ void launch_unpatchify(const float* tok, int c, int h, int w, int p, float* late
 void launch_silu_mul(const __nv_bfloat16* gu, int rows, int inter, __nv_bfloat16* out, cudaStream_t s) {
     silu_mul_kernel<<<grid_for((size_t)rows * inter / 2, 256), 256, 0, s>>>(gu, rows, inter, out);
 }
-void launch_cfg_euler(float* latents, const float* cond, const float* uncond, float gs, float d, int rows, int lw,
-                      int use_cfg, cudaStream_t s) {
-    cfg_euler_kernel<<<(rows + 7) / 8, 256, 0, s>>>(latents, cond, uncond, gs, d, rows, lw, use_cfg);
+void launch_cfg_euler(float* latents, const float* cond, const float* uncond, float gs, const float* sched,
+                      const int* counter, int rows, int lw, int use_cfg, cudaStream_t s) {
+    cfg_euler_kernel<<<(rows + 7) / 8, 256, 0, s>>>(latents, cond, uncond, gs, sched, counter, rows, lw, use_cfg);
 }
 void launch_add_bias_rows(float* y, const float* bias, size_t rows, int cols, cudaStream_t s) {
     add_bias_rows_kernel<<<grid_for(rows * cols, 256), 256, 0, s>>>(y, bias, rows, cols);

@@ -62,8 +62,12 @@ int make_tensor_map_2d(CUtensorMap* out, const void* base, int elem_bytes, uint6
 }
 
 // ---------------- buffers ----------------
+static std::atomic<uint64_t> g_alloc_epoch{1};
+uint64_t alloc_epoch() { return g_alloc_epoch.load(); }
+
 int DevBuf::ensure(size_t bytes) {
     if (bytes <= cap && p) return OK;
+    g_alloc_epoch++;
     if (p) cudaFree(p);
     p = nullptr;
     cap = 0;
@@ -77,6 +81,7 @@ int DevBuf::ensure(size_t bytes) {
     return OK;
 }
 void DevBuf::release() {
+    if (p) g_alloc_epoch++;
     if (p) cudaFree(p);
     p = nullptr;
     cap = 0;
@@ -106,6 +111,10 @@ int ctx_set_device(int device) {
         CMFC_CUDA(cudaMalloc(&c->status, 4));
         CMFC_CUDA(cudaMemset(c->status, 0, 4));
         CMFC_CUDA(cudaMallocHost(&c->status_host, 4));
+        CMFC_CUDA(cudaMalloc(&c->sched, (2 * Context::MAX_STEPS + 1) * 4));
+        CMFC_CUDA(cudaMemset(c->sched, 0, (2 * Context::MAX_STEPS + 1) * 4));
+        c->step_counter = reinterpret_cast<int*>(c->sched + 2 * Context::MAX_STEPS);
+        CMFC_CUDA(cudaMallocHost(&c->sched_host, (2 * Context::MAX_STEPS + 1) * 4));
         // log2f / exp2f of every half-precision value, from the host's libm: the device
         // quantizer must land on the bits the CPU encoder computes.
         std::vector<float> l2(65536), e2(65536);
@@ -551,28 +560,33 @@ int dev_gemm(Context* c, DevWeight* w, const __nv_bfloat16* x, int M, void* out,
 // segment (8-aligned, so every TMA x coordinate is a multiple of 16 bytes).  Re-uploaded only
 // when the segmentation changes.
 int prepare_segs(Context* c, const std::vector<int>& segs, SegTable* out) {
-    SegTable& st = c->segs;
-    if (st.host != segs || !st.dev) {
-        std::vector<int> tab(2 * segs.size() + 1, 0);
-        int mx = 0, col = 0;
-        for (size_t i = 0; i < segs.size(); ++i) {
-            if (segs[i] <= 0) return fail(ERR_BAD_ARG, "empty segment");
-            tab[i + 1] = tab[i] + segs[i];
-            tab[segs.size() + 1 + i] = col;
-            col += (segs[i] + 7) & ~7;
-            mx = segs[i] > mx ? segs[i] : mx;
-        }
-        DevBuf& sb = c->buf("seg_table");
-        CMFC_TRY(sb.ensure(tab.size() * 4));
-        CMFC_CUDA(cudaMemcpyAsync(sb.p, tab.data(), tab.size() * 4, cudaMemcpyHostToDevice, c->stream));
-        CMFC_CUDA(cudaStreamSynchronize(c->stream));  // tab is a stack temporary
-        st.host = segs;
-        st.dev = sb.as<int>();
-        st.n_total = tab[segs.size()];
-        st.vt_pitch = col;
-        st.max_seg = mx;
+    for (auto& e : c->seg_cache)
+        if (e.first.host == segs) { *out = e.first; return OK; }
+    std::vector<int> tab(2 * segs.size() + 1, 0);
+    int mx = 0, col = 0;
+    for (size_t i = 0; i < segs.size(); ++i) {
+        if (segs[i] <= 0) return fail(ERR_BAD_ARG, "empty segment");
+        tab[i + 1] = tab[i] + segs[i];
+        tab[segs.size() + 1 + i] = col;
+        col += (segs[i] + 7) & ~7;
+        mx = segs[i] > mx ? segs[i] : mx;
     }
-    *out = st;
+    if (c->seg_cache.size() >= 8) {  // a forward alternates between two or three segmentations
+        CMFC_CUDA(cudaStreamSynchronize(c->stream));
+        c->seg_cache.front().second.release();
+        c->seg_cache.erase(c->seg_cache.begin());
+    }
+    c->seg_cache.emplace_back();
+    auto& e = c->seg_cache.back();
+    CMFC_TRY(e.second.ensure(tab.size() * 4));
+    CMFC_CUDA(cudaMemcpyAsync(e.second.p, tab.data(), tab.size() * 4, cudaMemcpyHostToDevice, c->stream));
+    CMFC_CUDA(cudaStreamSynchronize(c->stream));  // tab is a stack temporary
+    e.first.host = segs;
+    e.first.dev = e.second.as<int>();
+    e.first.n_total = tab[segs.size()];
+    e.first.vt_pitch = col;
+    e.first.max_seg = mx;
+    *out = e.first;
     return OK;
 }
 

@@ -16,6 +16,10 @@ namespace cmfc {
 enum : int { DT_F32 = 0, DT_F16 = 1, DT_U8 = 6, DT_Q8 = 3, DT_Q4T = 11, DT_Q4TP = 15 };
 
 // ---- growable device buffer (no allocation in steady state) ----
+// Bumped whenever a device buffer is (re)allocated or freed: a captured CUDA graph holds raw
+// pointers, so a graph captured under an older epoch must not be replayed.
+uint64_t alloc_epoch();
+
 struct DevBuf {
     void* p = nullptr;
     size_t cap = 0;
@@ -76,9 +80,14 @@ struct Context {
     int num_sms = 0;
     uint32_t* status = nullptr;       // device status word for bounded-wait kernels
     uint32_t* status_host = nullptr;  // pinned mirror
+    // denoise schedule on the device: [2 * MAX_STEPS] floats (t_i, d_i) followed by the step counter
+    static constexpr int MAX_STEPS = 1024;
+    float* sched = nullptr;
+    int* step_counter = nullptr;
+    float* sched_host = nullptr;      // pinned staging, 2 * MAX_STEPS floats + 1 int
     std::map<std::tuple<uint64_t, int64_t, int64_t, int64_t, int>, std::unique_ptr<DevWeight>> weights;
     std::map<std::string, DevBuf> ws;  // named workspaces
-    SegTable segs;
+    std::vector<std::pair<SegTable, DevBuf>> seg_cache;  // a few recent segmentations, each with its device table
     DevBuf resident_x;                 // hidden state kept between chained dit_block_seg calls
     size_t resident_len = 0;
     float* log2_lut = nullptr;         // [65536] log2f of every f16 value (host libm)
