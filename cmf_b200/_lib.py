@@ -56,6 +56,19 @@ SYMBOLS = {
     "cmfc_nextdit_forward_pair_taps": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p,
                                                  C.c_size_t, C.c_void_p, C.c_size_t, C.c_float, C.c_void_p,
                                                  C.c_void_p, C.c_void_p]),
+    "cmfc_vae_create": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
+    "cmfc_vae_destroy": (None, [C.c_void_p]),
+    "cmfc_vae_info": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32), C.POINTER(C.c_float),
+                                C.POINTER(C.c_float)]),
+    "cmfc_vae_decode": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p]),
+    "cmfc_vae_decode_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p]),
+    "cmfc_vae_conv2d": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t,
+                                  C.c_size_t, C.c_size_t, C.c_void_p]),
+    "cmfc_vae_upsample_conv": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t,
+                                         C.c_size_t, C.c_size_t, C.c_void_p]),
+    "cmfc_bench_vae_decode": (C.c_int, [C.c_void_p, C.c_size_t, C.c_size_t, C.c_int, C.POINTER(C.c_float)]),
+    "cmfc_bench_conv": (C.c_int, [C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t, C.c_int, C.c_int,
+                                  C.POINTER(C.c_float)]),
     "cmfc_denoise": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p, C.c_size_t,
                                C.c_void_p, C.c_size_t, C.c_uint32, C.c_float]),
     "cmfc_denoise_begin": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p,

@@ -286,4 +286,7 @@ __device__ __forceinline__ double warp_sum(double v) {
 int make_tensor_map_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t rows, uint64_t cols,
                        uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols, int swizzle);
 
+int make_tensor_map_nhwc16(CUtensorMap* out, const void* base, uint64_t channels, uint64_t width, uint64_t height,
+                           uint64_t pixel_pitch_bytes, uint32_t box_c, uint32_t box_w, uint32_t box_h, int swizzle);
+
 }  // namespace cmfc

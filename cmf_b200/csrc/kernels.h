@@ -3,6 +3,7 @@
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -106,5 +107,58 @@ void launch_v_head_major_to_vt(const float* v_head_major, int nkv, int n, int hd
 void launch_add_bias_rows(float* y, const float* bias, size_t rows, int cols, cudaStream_t s);
 void launch_fill_normal(float* out, size_t n, uint64_t seed, float std, cudaStream_t s);
 void launch_interleave_f32(float* dst, int dst_stride, int dst_off, const float* src, size_t count, cudaStream_t s);
+
+// ---------------- VAE decoder: split-f16 implicit-GEMM convolution (conv_f16x2.cu) ----------------
+// A "split" tensor is an f32 tensor stored as two f16 planes, hi = f16(v) and lo = f16(v - hi).
+struct ConvParams {
+    int ic;                  // input channels as stored (padded to a multiple of 32)
+    int taps;                // 9 (3x3, padding 1) or 1 (1x1 / linear)
+    int w, h;                // output = input extent in pixels; a linear over n tokens has w = n, h = 1
+    int bw, bh;              // pixel tile, bw * bh = 256, bw a power of two
+    int oc;                  // output channels (rows of the weight planes)
+    int a_planes, b_planes;  // 1: hi only, 2: hi + lo
+    const float* bias;       // [oc] or null
+    float out_scale;         // applied to (acc + bias)
+    const float* residual;   // f32, same indexing as the output, or null
+    float* out_f32;          // any of the two outputs may be null
+    __half *out_hi, *out_lo;
+    int out_pitch;           // elements between pixels (pixel-major) or between channels (channel-major)
+    int channel_major;       // 0: out[pixel * pitch + oc] (NHWC); 1: out[oc * pitch + pixel] (NCHW / V^T)
+    int tiles_oc, tiles_x, tiles_y;  // filled by the launcher
+    uint32_t* status;
+};
+int launch_conv_f16x2(const CUtensorMap& tm_a_hi, const CUtensorMap& tm_a_lo, const CUtensorMap& tm_b_hi,
+                      const CUtensorMap& tm_b_lo, ConvParams p, int num_sms, cudaStream_t stream);
+
+// ---------------- VAE decoder: memory-bound passes (vae_kernels.cu) ----------------
+// GroupNorm (eps 1e-6, f64 statistics) over NHWC f32 x [pixels, c], c a power of two in [32, 1024].
+// stats: gn_stats_bytes(c) bytes; the first [c][2] doubles receive (sum, sum of squares) per
+// channel, the rest is scratch for per-block partials that are reduced in a fixed order.
+size_t gn_stats_bytes(int c);
+int launch_gn_stats(const float* x, size_t pixels, int c, double* stats, cudaStream_t s);
+// y = ((x - mean_g) * inv_g) as f32 * w + b, optional SiLU, written as split planes; when raw_hi is
+// given the unnormalized x is also written as split planes (the input of a shortcut convolution).
+int launch_gn_apply(const float* x, size_t pixels, int c, int groups, const double* stats, const float* w,
+                    const float* b, int silu, __half* y_hi, __half* y_lo, __half* raw_hi, __half* raw_lo,
+                    cudaStream_t s);
+// nearest 2x upsampling of NHWC f32 [h, w, c] into split planes [2h, 2w, c]
+void launch_upsample2x_split(const float* x, int h, int w, int c, __half* hi, __half* lo, cudaStream_t s);
+// NCHW f32 [c, h*w] -> split NHWC planes [h*w, c_pad] with v * mul + add (pad channels zero)
+void launch_nchw_to_split(const float* x, int c, size_t pixels, int c_pad, float div, float add, int affine,
+                          __half* hi, __half* lo, cudaStream_t s);
+// NHWC f32 [pixels, c] <-> NCHW f32 [c, pixels]
+void launch_nhwc_to_nchw(const float* x, size_t pixels, int c, float* out, cudaStream_t s);
+void launch_nchw_to_nhwc(const float* x, size_t pixels, int c, float* out, cudaStream_t s);
+// OIHW f32 [oc, ic, k, k] -> split planes [oc, k*k, ic_pad]
+void launch_conv_weight_split(const float* w, int oc, int ic, int taps, int ic_pad, __half* hi, __half* lo,
+                              cudaStream_t s);
+// row softmax of f32 scores [rows, cols] (row pitch ld) into split planes with row pitch ldp
+int launch_softmax_rows_split(const float* scores, size_t rows, int cols, size_t ld, __half* hi, __half* lo,
+                              size_t ldp, cudaStream_t s);
+// f32 -> split planes, element-wise
+void launch_split_f32(const float* x, size_t n, __half* hi, __half* lo, cudaStream_t s);
+// group-normalized f32 output (no split): y = ((x - mean) * inv) as f32 * w + b, optional SiLU
+int launch_gn_apply_f32(const float* x, size_t pixels, int c, int groups, const double* stats, const float* w,
+                        const float* b, int silu, float* y, cudaStream_t s);
 
 }  // namespace cmfc

@@ -61,6 +61,30 @@ int make_tensor_map_2d(CUtensorMap* out, const void* base, int elem_bytes, uint6
     return OK;
 }
 
+// 3-D tiled map over an NHWC plane of 2-byte elements: dims (channels, width, height), box
+// (box_c, box_w, box_h); out-of-range coordinates read as zero.  swizzle as in make_tensor_map_2d.
+int make_tensor_map_nhwc16(CUtensorMap* out, const void* base, uint64_t channels, uint64_t width, uint64_t height,
+                           uint64_t pixel_pitch_bytes, uint32_t box_c, uint32_t box_w, uint32_t box_h, int swizzle) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return fail(ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[3] = {channels, width, height};
+    cuuint64_t strides[2] = {pixel_pitch_bytes, pixel_pitch_bytes * width};
+    cuuint32_t box[3] = {box_c, box_w, box_h};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUtensorMapSwizzle sw = swizzle == 3 ? CU_TENSOR_MAP_SWIZZLE_128B
+                            : swizzle == 2 ? CU_TENSOR_MAP_SWIZZLE_64B
+                            : swizzle == 1 ? CU_TENSOR_MAP_SWIZZLE_32B
+                                           : CU_TENSOR_MAP_SWIZZLE_NONE;
+    if ((reinterpret_cast<uintptr_t>(base) & 15) || (pixel_pitch_bytes & 15))
+        return fail(ERR_BAD_ARG, "tensor map base and pitch must be 16-byte aligned");
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(ERR_CUDA, "cuTensorMapEncodeTiled (3-D) failed with code " + std::to_string((int)r));
+    return OK;
+}
+
 // ---------------- buffers ----------------
 static std::atomic<uint64_t> g_alloc_epoch{1};
 uint64_t alloc_epoch() { return g_alloc_epoch.load(); }
@@ -463,6 +487,9 @@ int upload_f32(Context* c, Model* m, int64_t idx, DevWeight** out) {
     } else {
         return fail(ERR_UNSUPPORTED, "tensor " + t.name + ": expected f32 or f16, found dtype " + std::to_string(t.dtype));
     }
+    // a copy from pageable memory may return before its DMA lands; readers run on c->stream,
+    // which is not ordered after the legacy default stream
+    CMFC_CUDA(cudaStreamSynchronize(0));
     *out = w.get();
     c->weights[key] = std::move(w);
     return OK;

@@ -234,6 +234,18 @@ def bench_rowop(kind, rows, cols, iters=10):
     return ms.value, nb.value
 
 
+def bench_vae_decode(vae, h, w, iters=3):
+    ms = C.c_float()
+    check(lib().cmfc_bench_vae_decode(vae.handle, h, w, iters, C.byref(ms)))
+    return float(ms.value)
+
+
+def bench_conv(ic, oc, h, w, k=3, a_planes=1, iters=5):
+    ms = C.c_float()
+    check(lib().cmfc_bench_conv(ic, oc, h, w, k, a_planes, iters, C.byref(ms)))
+    return float(ms.value)
+
+
 def profile_enable(on=True):
     check(lib().cmfc_profile_enable(int(on)))
 

@@ -80,3 +80,103 @@ def write_model(path, cfg, attn="q8", ffn="q8", seed=0, std=0.02):
     w.write(tmp, hash_tensors=False)
     os.replace(tmp, path)
     return path
+
+
+# ---------------------------------------------------------------------------------------------
+# Synthetic FLUX-class VAE decoder (diffusers AutoencoderKL naming, crates/cortiq-engine/src/vae.rs
+# from_tensors :549-633).  Host numpy only: about 50 M parameters at full size.
+FLUX_VAE = dict(block_out_channels=[128, 256, 512, 512], layers_per_block=2, latent_channels=16, norm_num_groups=32,
+                scaling_factor=0.3611, shift_factor=0.1159, out_channels=3)
+TINY_VAE = dict(block_out_channels=[32, 64], layers_per_block=1, latent_channels=16, norm_num_groups=32,
+                scaling_factor=0.3611, shift_factor=0.1159, out_channels=3)
+
+
+def vae_tensor_list(cfg):
+    """[(name without the 'vae.' prefix, shape, kind)]; kind 'k' conv kernel, 'l' linear weight,
+    'b' bias, 'g' norm gain, 'h' norm shift."""
+    rev = list(reversed(cfg["block_out_channels"]))
+    out = []
+
+    def conv(n, oc, ic, k):
+        out.append((n + ".weight", (oc, ic, k, k), "k"))
+        out.append((n + ".bias", (oc,), "b"))
+
+    def norm(n, c):
+        out.append((n + ".weight", (c,), "g"))
+        out.append((n + ".bias", (c,), "h"))
+
+    def resnet(n, cin, cout):
+        norm(n + ".norm1", cin)
+        conv(n + ".conv1", cout, cin, 3)
+        norm(n + ".norm2", cout)
+        conv(n + ".conv2", cout, cout, 3)
+        if cin != cout:
+            conv(n + ".conv_shortcut", cout, cin, 1)
+
+    c0 = rev[0]
+    conv("decoder.conv_in", c0, cfg["latent_channels"], 3)
+    resnet("decoder.mid_block.resnets.0", c0, c0)
+    a = "decoder.mid_block.attentions.0"
+    norm(a + ".group_norm", c0)
+    for p in ("to_q", "to_k", "to_v", "to_out.0"):
+        out.append((f"{a}.{p}.weight", (c0, c0), "l"))
+        out.append((f"{a}.{p}.bias", (c0,), "b"))
+    resnet("decoder.mid_block.resnets.1", c0, c0)
+    prev = c0
+    for b, ch in enumerate(rev):
+        for r in range(cfg["layers_per_block"] + 1):
+            resnet(f"decoder.up_blocks.{b}.resnets.{r}", prev if r == 0 else ch, ch)
+        prev = ch
+        if b != len(rev) - 1:
+            conv(f"decoder.up_blocks.{b}.upsamplers.0.conv", ch, ch, 3)
+    norm("decoder.conv_norm_out", prev)
+    conv("decoder.conv_out", cfg["out_channels"], prev, 3)
+    return out
+
+
+def vae_tensors(cfg, seed=0):
+    """{name: f32 array} of a synthetic decoder.  Conv kernels are rounded to f16 values (the
+    packer stores them as f16, crates/cortiq-cli/src/imagepack.rs:181-205), scaled so that
+    activations keep unit order of magnitude through the stack."""
+    rng = np.random.default_rng(seed * 7919 + 17)
+    t = {}
+    for name, shape, kind in vae_tensor_list(cfg):
+        if kind == "k":
+            fan_in = shape[1] * shape[2] * shape[3]
+            a = rng.standard_normal(shape, np.float32) * np.float32(1.0 / np.sqrt(fan_in))
+            a = a.astype(np.float16).astype(np.float32)
+        elif kind == "l":
+            a = rng.standard_normal(shape, np.float32) * np.float32(1.0 / np.sqrt(shape[1]))
+        elif kind == "g":
+            a = 1.0 + 0.1 * rng.standard_normal(shape, np.float32)
+        else:
+            a = 0.05 * rng.standard_normal(shape, np.float32)
+        t[name] = a.astype(np.float32)
+    return t
+
+
+def vae_config_json(cfg):
+    return {k: cfg[k] for k in ("block_out_channels", "layers_per_block", "latent_channels", "norm_num_groups",
+                                "scaling_factor", "shift_factor", "out_channels")}
+
+
+def add_vae(writer, cfg, seed=0):
+    """Append vae.* tensors and vae.config_json to a CmfWriter: 4-D kernels as f16, the rest f32."""
+    from .container import DT_F16
+    for name, a in vae_tensors(cfg, seed).items():
+        if a.ndim == 4:
+            h = np.ascontiguousarray(a.astype(np.float16))
+            writer.add("vae." + name, DT_F16, a.shape, h.view(np.uint8).reshape(-1))
+        else:
+            writer.add_f32("vae." + name, a)
+    writer.add_json("vae.config_json", vae_config_json(cfg))
+
+
+def write_vae_model(path, cfg, seed=0):
+    w = CmfWriter(arch={"arch_name": "flux-vae-synth", "hidden_size": 0, "num_layers": 0, "vocab_size": 0},
+                  quant_type="f16")
+    add_vae(w, cfg, seed)
+    tmp = path + f".tmp{os.getpid()}"
+    w.write(tmp, hash_tensors=False)
+    os.replace(tmp, path)
+    return path

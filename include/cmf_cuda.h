@@ -45,6 +45,7 @@ extern "C" {
 
 typedef struct cmfc_model cmfc_model;     /* an opened, memory-mapped .cmf container */
 typedef struct cmfc_nextdit cmfc_nextdit; /* a NextDiT bound to a model, weights resident */
+typedef struct cmfc_vae cmfc_vae;         /* a VAE decoder bound to a model, weights resident */
 
 /* Thread-local message of the last failing call on this thread
  * (style of crates/cortiq-ffi/include/cortiq.h:5-7, cortiq_last_error). */
@@ -166,6 +167,31 @@ int cmfc_denoise_begin(cmfc_nextdit* d, const float* latents, size_t batch, size
 int cmfc_denoise_step(cmfc_nextdit* d, uint32_t i);
 int cmfc_denoise_end(cmfc_nextdit* d, float* latents);
 
+/* ---- VAE decoder (crates/cortiq-engine/src/vae.rs): latents [latent_channels, h, w] at model
+ * scale -> RGB [3, s*h, s*w] in [-1, 1], s = 2^(up blocks with an upsampler), 8 for FLUX.
+ * f32 semantics: every GEMM operand is carried as two f16 planes (hi + lo), accumulation in f32;
+ * GroupNorm statistics in f64 as in vae.rs:270-294. ---- */
+
+/* VaeDecoder::from_cmf (vae.rs:524-548): reads vae.config_json (norm_num_groups, latent_channels,
+ * scaling_factor, shift_factor) and the vae.decoder.* tensors (f16 conv kernels, f32 the rest) */
+int cmfc_vae_create(cmfc_model* m, cmfc_vae** out);
+void cmfc_vae_destroy(cmfc_vae* v);
+/* any out pointer may be null */
+int cmfc_vae_info(const cmfc_vae* v, uint32_t* latent_channels, uint32_t* upscale, float* scaling_factor,
+                  float* shift_factor);
+/* VaeDecoder::decode (vae.rs:637-690): host z [latent_channels, h, w] -> host out [3, s*h, s*w] */
+int cmfc_vae_decode(cmfc_vae* v, const float* z, size_t h, size_t w, float* out);
+/* the same on device pointers (both f32, caller-owned); returns after the stream has drained */
+int cmfc_vae_decode_device(cmfc_vae* v, const float* d_z, size_t h, size_t w, float* d_out);
+/* gpu::vae_conv2d (gpu.rs:2026-2046): w [oc, ic, k, k], bias [oc], x [ic, h, w_img] -> out
+ * [oc, h, w_img]; k is 1 or 3, padding k/2.  Host pointers. */
+int cmfc_vae_conv2d(const float* w, const float* bias, const float* x, size_t ic, size_t oc, size_t h, size_t w_img,
+                    size_t k, float* out);
+/* gpu::vae_upsample_conv (gpu.rs:2002-2022): nearest 2x upsampling of x [ic, h, w_img], then the
+ * convolution -> out [oc, 2h, 2w_img].  ic must be a multiple of 32. */
+int cmfc_vae_upsample_conv(const float* w, const float* bias, const float* x, size_t ic, size_t oc, size_t h,
+                           size_t w_img, size_t k, float* out);
+
 /* ---- quantizers on the device, byte-identical to the reference encoders
  * (crates/cortiq-cli/src/convert.rs:551-566 encode_q8_row, :597-613 encode_q4_tiled,
  * :883-992 encode_q4tp).  w [rows, cols] host f32 -> payload (host, caller-sized with
@@ -208,6 +234,11 @@ int cmfc_bench_attention(size_t nh, size_t nkv, size_t hd, size_t n, size_t nseg
  * launch.  kind: 0 modulated RMSNorm, 1 gated residual, 2 gated residual + next modulated norm
  * (one pass), 3 qk-norm + RoPE + head packing. */
 int cmfc_bench_rowop(int kind, size_t rows, size_t cols, int iters, float* ms_per_launch, double* bytes_per_launch);
+/* Time whole VAE decodes of a synthetic latent [latent_channels, h, w] resident on the device. */
+int cmfc_bench_vae_decode(cmfc_vae* v, size_t h, size_t w, int iters, float* ms_per_decode);
+/* Time the implicit-GEMM convolution ic -> oc (k x k, k 1 or 3) over an h x w image of synthetic
+ * split planes; a_planes 1 = f16 kernels (two MMA passes), 2 = f32 kernels (three). */
+int cmfc_bench_conv(size_t ic, size_t oc, size_t h, size_t w, size_t k, int a_planes, int iters, float* ms_per_launch);
 /* the cudaStream_t every kernel of the current device's context is launched on (so a caller can
  * record its own events around library work) */
 void* cmfc_stream_handle(void);
