@@ -173,6 +173,20 @@ conv_f16x2_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_cons
                 tmem_ld_x32(tmem + acc * CV_PIX + lane_addr + c * 32, v);
                 tc_wait_ld();
                 if (!live) continue;
+                // The output may alias the residual (a block adds into its own input), so the
+                // compiler cannot move a residual load above an earlier store: gather the chunk's
+                // 32 residual values first, then store.
+                float res[32];
+                if (p.residual) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int pi = c * 32 + j;
+                        const int px = x0 + (pi & bw_mask), py = y0 + (pi >> bw_shift);
+                        const size_t pix = (size_t)py * p.w + px;
+                        const size_t o = p.channel_major ? (size_t)oc * p.out_pitch + pix : pix * p.out_pitch + oc;
+                        res[j] = (px < p.w && py < p.h) ? p.residual[o] : 0.0f;
+                    }
+                }
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                     const int pi = c * 32 + j;
@@ -181,7 +195,7 @@ conv_f16x2_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_cons
                         const size_t pix = (size_t)py * p.w + px;
                         const size_t o = p.channel_major ? (size_t)oc * p.out_pitch + pix : pix * p.out_pitch + oc;
                         float val = (__uint_as_float(v[j]) + bias) * p.out_scale;
-                        if (p.residual) val += p.residual[o];
+                        if (p.residual) val += res[j];
                         if (p.out_f32) p.out_f32[o] = val;
                         if (p.out_hi) split_store(p.out_hi, p.out_lo, o, val);
                     }

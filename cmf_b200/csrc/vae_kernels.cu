@@ -66,13 +66,15 @@ __global__ void __launch_bounds__(256) gn_stats_kernel(const float4* __restrict_
     }
 }
 
-// partials [blocks][2c] -> stats [2c]
+// partials [blocks][2c] -> stats [2c].  One warp per output: lane l adds blocks l, l + 32, ... in
+// order, then the lanes are combined by a fixed butterfly, so the result does not depend on timing.
 __global__ void gn_finalize_kernel(const double* __restrict__ partials, int blocks, int c2, double* __restrict__ stats) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (i >= c2) return;
     double a = 0;
-    for (int b = 0; b < blocks; ++b) a += partials[(size_t)b * c2 + i];
-    stats[i] = a;
+    for (int b = lane; b < blocks; b += 32) a += partials[(size_t)b * c2 + i];
+    a = warp_sum(a);
+    if (lane == 0) stats[i] = a;
 }
 
 // ---- GroupNorm apply (+ SiLU) ----
@@ -265,7 +267,7 @@ int launch_gn_stats(const float* x, size_t pixels, int c, double* stats, cudaStr
     const int blocks = grid_for(pixels, ppb * 8);
     double* partials = stats + 2 * c;
     gn_stats_kernel<<<blocks, 256, 0, s>>>(reinterpret_cast<const float4*>(x), pixels, c / 4, partials);
-    gn_finalize_kernel<<<(2 * c + 127) / 128, 128, 0, s>>>(partials, blocks, 2 * c, stats);
+    gn_finalize_kernel<<<(2 * c + 7) / 8, 256, 0, s>>>(partials, blocks, 2 * c, stats);
     CMFC_CUDA(cudaGetLastError());
     return OK;
 }
