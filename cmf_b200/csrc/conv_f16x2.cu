@@ -33,7 +33,7 @@ constexpr int CV_A_BYTES = CV_OC * CV_K * 2;    // 8 KiB per plane
 constexpr int CV_B_BYTES = CV_PIX * CV_K * 2;   // 16 KiB per plane
 constexpr int CV_RING_BYTES = 5 * (CV_A_BYTES + 2 * CV_B_BYTES);  // 200 KiB
 constexpr int CV_SMEM = CV_RING_BYTES + 1024 + 256;
-constexpr int CV_THREADS = 32 * 6;              // TMA, MMA, four epilogue warps
+constexpr int CV_THREADS = 32 * 10;             // TMA, MMA, eight epilogue warps
 
 struct ConvBars {
     uint64_t full[CV_MAX_STAGES], empty[CV_MAX_STAGES], acc_full[2], acc_empty[2];
@@ -58,6 +58,8 @@ __device__ __forceinline__ void split_store(__half* hi, __half* lo, size_t o, fl
     lo[o] = __float2half_rn(v - __half2float(h));
 }
 
+// BW: the tile's width in pixels when it is 16 (images) or 256 (token rows); 0 = read it from p.bw
+template <int BW>
 __global__ void __launch_bounds__(CV_THREADS, 1)
 conv_f16x2_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ CUtensorMap tm_a_lo,
                   const __grid_constant__ CUtensorMap tm_b_hi, const __grid_constant__ CUtensorMap tm_b_lo,
@@ -83,7 +85,7 @@ conv_f16x2_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_cons
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&bars->acc_full[a], 1);
-            mbar_init(&bars->acc_empty[a], 4);
+            mbar_init(&bars->acc_empty[a], 8);
         }
         bars->abort_flag = 0;
         mbar_fence_init();
@@ -153,53 +155,89 @@ conv_f16x2_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_cons
             }
         }
     } else {
-        // epilogue: this thread owns output channel oc0 + row and walks the tile's 256 pixels
-        const int quarter = warp & 3;
+        // epilogue, eight warps: warp w may touch TMEM lanes 32 * (w % 4); the two warps of a lane
+        // quarter split the tile's 256 pixel columns.  A thread owns output channel oc0 + row.
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
         const int row = quarter * 32 + lane;
-        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        const uint32_t lane_addr = ((uint32_t)(quarter * 32) << 16) + half * (CV_PIX / 2);
+        const size_t step_x = p.channel_major ? 1 : (size_t)p.out_pitch;
+        const size_t step_y = (size_t)p.w * step_x;
         uint32_t lt = 0;
         for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++lt) {
             const uint32_t acc = lt & 1u, aph = (lt >> 1) & 1u;
             const int oc = (tile % p.tiles_oc) * CV_OC + row;
             const int r = tile / p.tiles_oc;
             const int x0 = (r % p.tiles_x) * p.bw, y0 = (r / p.tiles_x) * p.bh;
-            if (!mbar_wait<200>(&bars->acc_full[acc], aph, abort_flag, 33)) break;
-            tc_fence_after();
+            const int xlim = p.w - x0, ylim = p.h - y0;  // tile-relative extent of the image
             const bool live = oc < p.oc;
-            const float bias = (p.bias && live) ? p.bias[oc] : 0.0f;
-#pragma unroll 1
-            for (int c = 0; c < CV_PIX / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld_x32(tmem + acc * CV_PIX + lane_addr + c * 32, v);
-                tc_wait_ld();
-                if (!live) continue;
-                // The output may alias the residual (a block adds into its own input), so the
-                // compiler cannot move a residual load above an earlier store: gather the chunk's
-                // 32 residual values first, then store.
-                float res[32];
-                if (p.residual) {
+            const float bias_s = (p.bias && live) ? p.bias[oc] * p.out_scale : 0.0f;
+            const size_t base = p.channel_major ? (size_t)oc * p.out_pitch + (size_t)y0 * p.w + x0
+                                                : ((size_t)y0 * p.w + x0) * p.out_pitch + oc;
+            // visit the 32 pixels of chunk ``c``: f(j, inside, element offset)
+            auto for_chunk = [&](int c, auto&& f) {
+                if constexpr (BW == 0) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        const int pi = c * 32 + j;
-                        const int px = x0 + (pi & bw_mask), py = y0 + (pi >> bw_shift);
-                        const size_t pix = (size_t)py * p.w + px;
-                        const size_t o = p.channel_major ? (size_t)oc * p.out_pitch + pix : pix * p.out_pitch + oc;
-                        res[j] = (px < p.w && py < p.h) ? p.residual[o] : 0.0f;
+                        const int pi = c * 32 + j, dx = pi & bw_mask, dy = pi >> bw_shift;
+                        f(j, dx < xlim && dy < ylim, base + dy * step_y + dx * step_x);
+                    }
+                } else {
+                    constexpr int SEG = BW < 32 ? BW : 32, ROWS = 32 / SEG;
+                    const int dy0 = (c * 32) / BW, dx0 = (c * 32) % BW;
+#pragma unroll
+                    for (int rr = 0; rr < ROWS; ++rr) {
+                        size_t o = base + (size_t)(dy0 + rr) * step_y + (size_t)dx0 * step_x;
+                        const bool row_ok = dy0 + rr < ylim;
+#pragma unroll
+                        for (int xx = 0; xx < SEG; ++xx, o += step_x) f(rr * SEG + xx, row_ok && dx0 + xx < xlim, o);
                     }
                 }
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int pi = c * 32 + j;
-                    const int px = x0 + (pi & bw_mask), py = y0 + (pi >> bw_shift);
-                    if (px < p.w && py < p.h) {
-                        const size_t pix = (size_t)py * p.w + px;
-                        const size_t o = p.channel_major ? (size_t)oc * p.out_pitch + pix : pix * p.out_pitch + oc;
-                        float val = (__uint_as_float(v[j]) + bias) * p.out_scale;
+            };
+            // The residual does not depend on the accumulator: a chunk's values are fetched while
+            // the previous chunk is in flight.  (The output may alias the residual, so they are all
+            // read before any element of the chunk is written.)
+            float res_a[32], res_b[32];
+            auto fetch = [&](int c, float* dst) {
+                for_chunk(c, [&](int j, bool ok, size_t o) { dst[j] = (ok && live) ? p.residual[o] : 0.0f; });
+            };
+            double ssum = 0.0, ssq = 0.0;
+            auto emit = [&](int c, const uint32_t* v, const float* res) {
+                for_chunk(c, [&](int j, bool ok, size_t o) {
+                    if (ok) {
+                        float val = fmaf(__uint_as_float(v[j]), p.out_scale, bias_s);
                         if (p.residual) val += res[j];
                         if (p.out_f32) p.out_f32[o] = val;
                         if (p.out_hi) split_store(p.out_hi, p.out_lo, o, val);
+                        if (p.stats_partial) {
+                            const double d = (double)val;
+                            ssum += d;
+                            ssq += d * d;
+                        }
                     }
-                }
+                });
+            };
+            const int chunk0 = half * (CV_PIX / 64);
+            if (p.residual) fetch(chunk0, res_a);
+            if (!mbar_wait<200>(&bars->acc_full[acc], aph, abort_flag, 33)) break;
+            tc_fence_after();
+            const uint32_t t0 = tmem + acc * CV_PIX + lane_addr;
+#pragma unroll 1
+            for (int cc = 0; cc < CV_PIX / 64; cc += 2) {
+                uint32_t v[32];
+                tmem_ld_x32(t0 + cc * 32, v);
+                if (p.residual) fetch(chunk0 + cc + 1, res_b);
+                tc_wait_ld();
+                if (live) emit(chunk0 + cc, v, res_a);
+                tmem_ld_x32(t0 + (cc + 1) * 32, v);
+                if (p.residual && cc + 2 < CV_PIX / 64) fetch(chunk0 + cc + 2, res_a);
+                tc_wait_ld();
+                if (live) emit(chunk0 + cc + 1, v, res_b);
+            }
+            if (p.stats_partial && live) {
+                // slot = (pixel tile, column half); reduced in slot order by the GroupNorm finalize
+                double* slot = p.stats_partial + ((size_t)r * 2 + half) * (2 * (size_t)p.oc) + 2 * (size_t)oc;
+                slot[0] = ssum;
+                slot[1] = ssq;
             }
             tc_fence_before();
             __syncwarp();
@@ -217,6 +255,20 @@ conv_f16x2_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_cons
 
 }  // namespace
 
+void conv_tile_shape(int w, int h, int* bw, int* bh) {
+    if (h == 1) { *bw = CV_PIX; *bh = 1; return; }
+    int b = 16;
+    while (b > w) b >>= 1;
+    *bw = b;
+    *bh = CV_PIX / b;
+}
+
+size_t conv_stats_slots(int w, int h) {
+    int bw, bh;
+    conv_tile_shape(w, h, &bw, &bh);
+    return 2 * (size_t)((w + bw - 1) / bw) * ((h + bh - 1) / bh);
+}
+
 int launch_conv_f16x2(const CUtensorMap& tm_a_hi, const CUtensorMap& tm_a_lo, const CUtensorMap& tm_b_hi,
                       const CUtensorMap& tm_b_lo, ConvParams p, int num_sms, cudaStream_t stream) {
     if (p.ic <= 0 || p.ic % CV_K || p.bw * p.bh != CV_PIX || (p.taps != 1 && p.taps != 9))
@@ -228,7 +280,9 @@ int launch_conv_f16x2(const CUtensorMap& tm_a_hi, const CUtensorMap& tm_a_lo, co
     int dev = 0;
     CMFC_CUDA(cudaGetDevice(&dev));
     if (!configured[dev & 63]) {
-        CMFC_CUDA(cudaFuncSetAttribute(conv_f16x2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, CV_SMEM));
+        CMFC_CUDA(cudaFuncSetAttribute(conv_f16x2_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, CV_SMEM));
+        CMFC_CUDA(cudaFuncSetAttribute(conv_f16x2_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, CV_SMEM));
+        CMFC_CUDA(cudaFuncSetAttribute(conv_f16x2_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, CV_SMEM));
         configured[dev & 63] = true;
     }
     p.tiles_oc = (p.oc + CV_OC - 1) / CV_OC;
@@ -236,7 +290,12 @@ int launch_conv_f16x2(const CUtensorMap& tm_a_hi, const CUtensorMap& tm_a_lo, co
     p.tiles_y = (p.h + p.bh - 1) / p.bh;
     const long long ntiles = (long long)p.tiles_oc * p.tiles_x * p.tiles_y;
     const int grid = (int)std::min<long long>(ntiles, num_sms);
-    conv_f16x2_kernel<<<grid, CV_THREADS, CV_SMEM, stream>>>(tm_a_hi, tm_a_lo, tm_b_hi, tm_b_lo, p);
+    if (p.bw == 16)
+        conv_f16x2_kernel<16><<<grid, CV_THREADS, CV_SMEM, stream>>>(tm_a_hi, tm_a_lo, tm_b_hi, tm_b_lo, p);
+    else if (p.bw == 256)
+        conv_f16x2_kernel<256><<<grid, CV_THREADS, CV_SMEM, stream>>>(tm_a_hi, tm_a_lo, tm_b_hi, tm_b_lo, p);
+    else
+        conv_f16x2_kernel<0><<<grid, CV_THREADS, CV_SMEM, stream>>>(tm_a_hi, tm_a_lo, tm_b_hi, tm_b_lo, p);
     CMFC_CUDA(cudaGetLastError());
     return OK;
 }

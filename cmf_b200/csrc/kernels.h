@@ -124,9 +124,14 @@ struct ConvParams {
     __half *out_hi, *out_lo;
     int out_pitch;           // elements between pixels (pixel-major) or between channels (channel-major)
     int channel_major;       // 0: out[pixel * pitch + oc] (NHWC); 1: out[oc * pitch + pixel] (NCHW / V^T)
+    double* stats_partial;   // null, or [2 * tiles_x * tiles_y][oc][2]: per-slot sum and sum of squares of the
+                             // stored values per channel (input of the next GroupNorm), see conv_stats_slots
     int tiles_oc, tiles_x, tiles_y;  // filled by the launcher
     uint32_t* status;
 };
+// pixel tile chosen for an h x w image, and the number of statistics slots a launch fills
+void conv_tile_shape(int w, int h, int* bw, int* bh);
+size_t conv_stats_slots(int w, int h);
 int launch_conv_f16x2(const CUtensorMap& tm_a_hi, const CUtensorMap& tm_a_lo, const CUtensorMap& tm_b_hi,
                       const CUtensorMap& tm_b_lo, ConvParams p, int num_sms, cudaStream_t stream);
 
@@ -135,6 +140,8 @@ int launch_conv_f16x2(const CUtensorMap& tm_a_hi, const CUtensorMap& tm_a_lo, co
 // stats: gn_stats_bytes(c) bytes; the first [c][2] doubles receive (sum, sum of squares) per
 // channel, the rest is scratch for per-block partials that are reduced in a fixed order.
 size_t gn_stats_bytes(int c);
+// partials [slots][c][2] -> stats [c][2], summed in slot order
+void launch_gn_finalize(const double* partials, size_t slots, int c, double* stats, cudaStream_t s);
 int launch_gn_stats(const float* x, size_t pixels, int c, double* stats, cudaStream_t s);
 // y = ((x - mean_g) * inv_g) as f32 * w + b, optional SiLU, written as split planes; when raw_hi is
 // given the unnormalized x is also written as split planes (the input of a shortcut convolution).

@@ -184,6 +184,7 @@ struct ConvOut {
     int pitch = 0;          // 0: oc (pixel-major) / pixels (channel-major)
     int channel_major = 0;
     float scale = 1.0f;
+    bool stats = false;     // also leave the per-channel sum / sum of squares of the output in "vae.stats"
 };
 
 // a: weight-side planes as a [oc rows, taps * ic_pad] matrix (maps prebuilt); b: NHWC planes with
@@ -194,24 +195,32 @@ int run_gemm(Context* c, const CUtensorMap& tm_a_hi, const CUtensorMap& tm_a_lo,
     ConvParams p;
     memset(&p, 0, sizeof(p));
     p.ic = ic_pad; p.taps = taps; p.w = w; p.h = h;
-    if (h == 1) { p.bw = 256; p.bh = 1; }
-    else {
-        int bw = 16;
-        while (bw > w) bw >>= 1;
-        p.bw = bw; p.bh = 256 / bw;
-    }
+    conv_tile_shape(w, h, &p.bw, &p.bh);
     p.oc = oc; p.a_planes = a_planes; p.b_planes = b_planes;
     p.bias = bias; p.out_scale = o.scale; p.residual = o.residual;
     p.out_f32 = o.f32; p.out_hi = o.split.hi; p.out_lo = o.split.lo;
     p.channel_major = o.channel_major;
     p.out_pitch = o.pitch ? o.pitch : (o.channel_major ? w * h : oc);
     p.status = c->status;
+    double* stats = c->buf("vae.stats").as<double>();
+    const size_t slots = conv_stats_slots(w, h);
+    if (o.stats) {
+        if (c->buf("vae.stats").cap < (2048 + slots * 2 * (size_t)oc) * sizeof(double))
+            return fail(ERR_SHAPE, "conv: statistics scratch too small");
+        p.stats_partial = stats + 2048;
+    }
     CUtensorMap tm_b_hi, tm_b_lo;
     CMFC_TRY(make_tensor_map_nhwc16(&tm_b_hi, b.hi, b_c, w, h, (uint64_t)b_pitch * 2, 32, p.bw, p.bh, 2));
     tm_b_lo = tm_b_hi;
     if (b_planes == 2) CMFC_TRY(make_tensor_map_nhwc16(&tm_b_lo, b.lo, b_c, w, h, (uint64_t)b_pitch * 2, 32, p.bw, p.bh, 2));
     c->launches++;
-    return launch_conv_f16x2(tm_a_hi, tm_a_lo, tm_b_hi, tm_b_lo, p, c->num_sms, c->stream);
+    CMFC_TRY(launch_conv_f16x2(tm_a_hi, tm_a_lo, tm_b_hi, tm_b_lo, p, c->num_sms, c->stream));
+    if (o.stats) {
+        launch_gn_finalize(p.stats_partial, slots, oc, stats, c->stream);
+        CMFC_CUDA(cudaGetLastError());
+        c->launches++;
+    }
+    return OK;
 }
 
 int run_conv(Context* c, const ConvW& cw, const Planes& x, int x_c, int w, int h, const ConvOut& o) {
@@ -219,29 +228,35 @@ int run_conv(Context* c, const ConvW& cw, const Planes& x, int x_c, int w, int h
     return run_gemm(c, cw.tm_hi, cw.tm_lo, cw.a_planes, cw.oc, cw.ic_pad, cw.taps, cw.bias, x, 2, x_c, x_c, w, h, o);
 }
 
+// ``have_stats``: the convolution that produced x already left its channel statistics in "vae.stats"
 int group_norm(Context* c, const NormW& n, int groups, const float* x, size_t pixels, int silu, const Planes& y,
-               const Planes* raw) {
+               const Planes* raw, bool have_stats) {
     double* stats = c->buf("vae.stats").as<double>();
-    CMFC_TRY(launch_gn_stats(x, pixels, n.c, stats, c->stream));
+    if (!have_stats) {
+        CMFC_TRY(launch_gn_stats(x, pixels, n.c, stats, c->stream));
+        c->launches += 2;
+    }
     CMFC_TRY(launch_gn_apply(x, pixels, n.c, groups, stats, n.w, n.b, silu, y.hi, y.lo, raw ? raw->hi : nullptr,
                              raw ? raw->lo : nullptr, c->stream));
-    c->launches += 2;
+    c->launches++;
     return OK;
 }
 
 struct Work {
     float *x = nullptr, *t1 = nullptr, *t2 = nullptr;
     Planes s0, s1;
+    bool stats_ready = false;  // "vae.stats" holds the channel statistics of x
 };
 
 // x [pix, cin] -> [pix, cout]; the result lands in wk.x (buffers rotate)
 int run_resnet(Context* c, const cmfc_vae* v, const ResnetW& r, Work& wk, int w, int h) {
     const size_t pix = (size_t)w * h;
-    CMFC_TRY(group_norm(c, r.n1, v->groups, wk.x, pix, 1, wk.s0, r.has_sc ? &wk.s1 : nullptr));
+    CMFC_TRY(group_norm(c, r.n1, v->groups, wk.x, pix, 1, wk.s0, r.has_sc ? &wk.s1 : nullptr, wk.stats_ready));
     ConvOut o1;
     o1.f32 = wk.t1;
+    o1.stats = true;
     CMFC_TRY(run_conv(c, r.c1, wk.s0, r.n1.c, w, h, o1));
-    CMFC_TRY(group_norm(c, r.n2, v->groups, wk.t1, pix, 1, wk.s0, nullptr));
+    CMFC_TRY(group_norm(c, r.n2, v->groups, wk.t1, pix, 1, wk.s0, nullptr, true));
     if (r.has_sc) {
         ConvOut os;
         os.f32 = wk.t2;
@@ -249,14 +264,17 @@ int run_resnet(Context* c, const cmfc_vae* v, const ResnetW& r, Work& wk, int w,
         ConvOut o2;
         o2.f32 = wk.t2;
         o2.residual = wk.t2;
+        o2.stats = true;
         CMFC_TRY(run_conv(c, r.c2, wk.s0, r.n2.c, w, h, o2));
         std::swap(wk.x, wk.t2);
     } else {
         ConvOut o2;
         o2.f32 = wk.x;
         o2.residual = wk.x;
+        o2.stats = true;
         CMFC_TRY(run_conv(c, r.c2, wk.s0, r.n2.c, w, h, o2));
     }
+    wk.stats_ready = true;
     return OK;
 }
 
@@ -276,7 +294,7 @@ int run_attention(Context* c, const cmfc_vae* v, Work& wk, int w, int h) {
     const Planes ot{bo.as<__half>(), bo.as<__half>() + tok};
     const Planes vt{bvt.as<__half>(), bvt.as<__half>() + (size_t)ch * n_pad};
     const Planes pr{bp.as<__half>(), bp.as<__half>() + (size_t)n * n_pad};
-    CMFC_TRY(group_norm(c, v->attn_norm, v->groups, wk.x, (size_t)n, 0, wk.s0, nullptr));
+    CMFC_TRY(group_norm(c, v->attn_norm, v->groups, wk.x, (size_t)n, 0, wk.s0, nullptr, wk.stats_ready));
     ConvOut oq; oq.split = q;
     CMFC_TRY(run_conv(c, v->attn_q, wk.s0, ch, n, 1, oq));
     ConvOut ok; ok.split = k;
@@ -297,8 +315,9 @@ int run_attention(Context* c, const cmfc_vae* v, Work& wk, int w, int h) {
     CMFC_TRY(make_tensor_map_2d(&tv_lo, vt.lo, 2, ch, n, (uint64_t)n_pad * 2, 128, 32, 2));
     ConvOut oo; oo.split = ot;
     CMFC_TRY(run_gemm(c, tv_hi, tv_lo, 2, ch, n_pad, 1, nullptr, pr, 2, n, n_pad, n, 1, oo));
-    ConvOut of; of.f32 = wk.x; of.residual = wk.x;
+    ConvOut of; of.f32 = wk.x; of.residual = wk.x; of.stats = true;
     CMFC_TRY(run_conv(c, v->attn_o, ot, ch, n, 1, of));
+    wk.stats_ready = true;
     return OK;
 }
 
@@ -308,13 +327,17 @@ namespace {
 
 struct Sizes {
     size_t max_elems = 0;
+    size_t stats_doubles = 0;  // scratch of the fused GroupNorm statistics: slots x channels x 2
     int out_h = 0, out_w = 0;
 };
 
 // the largest activation (pixels x channels) the schedule touches, and the image extent
 Sizes plan(const cmfc_vae* v, int h, int w) {
     Sizes s;
-    auto see = [&](size_t pix, int ch) { s.max_elems = std::max(s.max_elems, pix * (size_t)ch); };
+    auto see = [&](size_t pix, int ch) {
+        s.max_elems = std::max(s.max_elems, pix * (size_t)ch);
+        s.stats_doubles = std::max(s.stats_doubles, conv_stats_slots(w, h) * 2 * (size_t)ch);
+    };
     size_t pix = (size_t)h * w;
     see(pix, v->conv_in.ic_pad);
     see(pix, v->conv_in.oc);
@@ -340,7 +363,7 @@ int decode_device(Context* c, cmfc_vae* v, const float* d_z, int h, int w, float
     if (sz.max_elems > (size_t)1 << 33) return fail(ERR_SHAPE, "vae_decode: latent too large");
     const char* names[5] = {"vae.x", "vae.t1", "vae.t2", "vae.s0", "vae.s1"};
     for (const char* n : names) CMFC_TRY(c->buf(n).ensure(sz.max_elems * 4));
-    CMFC_TRY(c->buf("vae.stats").ensure(gn_stats_bytes(1024)));
+    CMFC_TRY(c->buf("vae.stats").ensure(std::max(gn_stats_bytes(1024), (2048 + sz.stats_doubles) * sizeof(double))));
     Work wk;
     wk.x = c->buf("vae.x").as<float>();
     wk.t1 = c->buf("vae.t1").as<float>();
@@ -356,7 +379,9 @@ int decode_device(Context* c, cmfc_vae* v, const float* d_z, int h, int w, float
         c->launches++;
         ConvOut o;
         o.f32 = wk.x;
+        o.stats = true;
         CMFC_TRY(run_conv(c, v->conv_in, wk.s0, v->conv_in.ic_pad, w, h, o));
+        wk.stats_ready = true;
     }
     {
         SpanGuard g(c, "vae-mid");
@@ -376,6 +401,7 @@ int decode_device(Context* c, cmfc_vae* v, const float* d_z, int h, int w, float
             h *= 2; w *= 2;
             ConvOut o;
             o.f32 = wk.t1;
+            o.stats = true;
             CMFC_TRY(run_conv(c, u.up, wk.s0, u.up.ic, w, h, o));
             std::swap(wk.x, wk.t1);
         }
@@ -383,7 +409,7 @@ int decode_device(Context* c, cmfc_vae* v, const float* d_z, int h, int w, float
     {
         SpanGuard g(c, "vae-out");
         pix = (size_t)h * w;
-        CMFC_TRY(group_norm(c, v->norm_out, v->groups, wk.x, pix, 1, wk.s0, nullptr));
+        CMFC_TRY(group_norm(c, v->norm_out, v->groups, wk.x, pix, 1, wk.s0, nullptr, wk.stats_ready));
         ConvOut o;
         o.f32 = d_out;
         o.channel_major = 1;

@@ -261,6 +261,10 @@ bool gn_channels_ok(int c) { return c >= 32 && c <= 1024 && (c & (c - 1)) == 0; 
 
 size_t gn_stats_bytes(int c) { return sizeof(double) * 2 * (size_t)c * (1 + MAX_GRID); }
 
+void launch_gn_finalize(const double* partials, size_t slots, int c, double* stats, cudaStream_t s) {
+    gn_finalize_kernel<<<(2 * c + 7) / 8, 256, 0, s>>>(partials, (int)slots, 2 * c, stats);
+}
+
 int launch_gn_stats(const float* x, size_t pixels, int c, double* stats, cudaStream_t s) {
     if (!gn_channels_ok(c)) return fail(ERR_UNSUPPORTED, "group norm: channels must be a power of two in [32, 1024]");
     const int ppb = 256 / (c / 4);
