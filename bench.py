@@ -172,6 +172,48 @@ def cpu_baseline_sample(cfg):
     return d["cpu_baseline"]
 
 
+def vae_leg(args, lh, lw, peaks, cpu=True):
+    """The stage after the denoiser: FLUX-class VAE decode of one latent [16, lh, lw] (synthetic
+    weights of the real architecture).  Device-resident time, end-to-end time through the public
+    API with host buffers, and the CPU oracle on a bounded sample."""
+    from cmf_b200 import Model, VaeDecoder, gpu, synth
+    from cmf_b200.microbench import vae_flops
+    path = os.path.join(args.model_dir, "cmf_bench_flux_vae.cmf")
+    if not os.path.exists(path):
+        synth.write_vae_model(path, synth.FLUX_VAE, 0)
+    z = np.random.default_rng(5).standard_normal((16, lh, lw)).astype(np.float32)
+    with Model(path) as m:
+        dec = VaeDecoder(m)
+        dec.decode(z, lh, lw)                               # warm-up: buffers, first-use costs
+        ms = gpu.bench_vae_decode(dec, lh, lw, iters=5)     # CUDA events around 5 decodes, latent resident
+        t0 = time.time()
+        for _ in range(3):
+            img = dec.decode(z, lh, lw)
+        e2e_ms = (time.time() - t0) / 3 * 1e3
+        dec.close()
+    fl = vae_flops(synth.FLUX_VAE, lh, lw)
+    out = {"workload": f"FLUX-class VAE decoder, latent 16x{lh}x{lw} -> RGB {8 * lh}x{8 * lw}, f32 semantics "
+                       "(split-f16 operands, two MMA passes per convolution)",
+           "ms": ms, "images_per_s": 1e3 / ms, "conv_tflops": fl / (ms * 1e-3) / 1e12,
+           "tensor_tflops": 2 * fl / (ms * 1e-3) / 1e12, "tensor_peak": peaks["bf16_sustained"],
+           "e2e": {"ms": e2e_ms, "images_per_s": 1e3 / e2e_ms, "h2d_bytes": z.nbytes, "d2h_bytes": img.nbytes,
+                   "call": "cmf_b200.VaeDecoder(model).decode(z, h, w) with host buffers"}}
+    if cpu:
+        from oracle import vae as ovae
+        t = synth.vae_tensors(synth.FLUX_VAE, 0)
+        sh = 16
+        zs = z[:, :sh, :sh].copy()
+        t0 = time.time()
+        ovae.decode(t, synth.FLUX_VAE, zs)
+        dt = time.time() - t0
+        scale = (lh * lw) / float(sh * sh)
+        out["cpu_baseline"] = {"images_per_s": 1.0 / (dt * scale), "kind": "port", "cores": os.cpu_count(),
+                               "sample": f"oracle decode of a {sh}x{sh} latent crop ({dt:.2f} s, numpy f64 matmuls), "
+                                         f"scaled by the pixel ratio {scale:.0f} (convolutions are linear in pixels; "
+                                         "the attention block's quadratic term is left out, which favours the CPU)"}
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -182,6 +224,7 @@ def main():
     ap.add_argument("--codec", default="q4t", choices=["q4t", "q4tp", "q8", "q4tp_ffn_q8_attn"])
     ap.add_argument("--latent", type=int, default=H, help="latent side (128 = 1024x1024 image, 256 = 2048x2048)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-vae", action="store_true", help="skip the VAE-decode leg (the stage after the denoiser)")
     ap.add_argument("--model-dir", default=os.environ.get("CMF_BENCH_DIR", tempfile.gettempdir()))
     args = ap.parse_args()
 
@@ -318,6 +361,11 @@ def main():
             except Exception as e:  # the baseline is a reported figure; its failure must not hide the GPU line
                 line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
                                         "sample": f"failed: {e!r}"}
+        if world == 1 and not args.no_vae:
+            try:
+                line["vae_decode"] = vae_leg(args, LH, LW, peaks, cpu=not args.no_cpu_baseline)
+            except Exception as e:  # a secondary figure: never hide the headline line
+                line["vae_decode"] = {"failed": repr(e)}
         if args.codec in ("q4t", "q4tp"):
             # dram__bytes_read.sum + dram__bytes_write.sum of one captured launch of this kernel, the
             # gate/up GEMM of a block (N=18432, K=2304, M=8704, SwiGLU epilogue; algorithmic 224 MB):
