@@ -12,3 +12,4 @@ from . import gpu  # noqa: F401
 from .container import CmfWriter, Model  # noqa: F401
 from .dit import NextDit, GenParams, denoise  # noqa: F401
 from .vae import VaeDecoder  # noqa: F401
+from .textenc import GemmaEncoder  # noqa: F401

@@ -69,6 +69,10 @@ SYMBOLS = {
     "cmfc_bench_vae_decode": (C.c_int, [C.c_void_p, C.c_size_t, C.c_size_t, C.c_int, C.POINTER(C.c_float)]),
     "cmfc_bench_conv": (C.c_int, [C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t, C.c_int, C.c_int,
                                   C.POINTER(C.c_float)]),
+    "cmfc_gemma_create": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
+    "cmfc_gemma_destroy": (None, [C.c_void_p]),
+    "cmfc_gemma_dims": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint32)]),
+    "cmfc_gemma_encode": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]),
     "cmfc_denoise": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p, C.c_size_t,
                                C.c_void_p, C.c_size_t, C.c_uint32, C.c_float]),
     "cmfc_denoise_begin": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p,

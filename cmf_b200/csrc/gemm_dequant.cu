@@ -111,6 +111,10 @@ __device__ __forceinline__ void unpack_q4t_word(uint32_t w, uint32_t hi2, uint32
 __device__ __forceinline__ uint4 lds128(const uint8_t* p) { return *reinterpret_cast<const uint4*>(p); }
 
 __device__ __forceinline__ float silu_f(float v) { return __fdividef(v, 1.0f + __expf(-v)); }
+// crates/cortiq-engine/src/textenc.rs:70-73
+__device__ __forceinline__ float gelu_tanh_f(float v) {
+    return 0.5f * v * (1.0f + tanhf(0.7978846f * (v + 0.044715f * v * v * v)));
+}
 
 // WKIND: 0 = q8 (int8 plane); 1 = q4tp (nibble plane + transposed f32 scales);
 //        2 = q4_tiled (nibble plane + transposed scales split into bf16 hi/lo halves)
@@ -316,6 +320,20 @@ gemm_dequant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
                         if (mb + j < p.M) out[(size_t)j * p.ldo] = __float2bfloat16_rn(__uint_as_float(v[j]) * rs);
+                } else if (p.mode == GEMM_OUT_GEGLU) {
+                    // as GEMM_OUT_SWIGLU below, with the tanh-form GELU on the gate
+                    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)mb * p.ldo + (n >> 1);
+                    const bool odd = lane & 1;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) {
+                        float mine_a = __uint_as_float(v[j]), mine_b = __uint_as_float(v[j + 1]);
+                        if (WKIND == 0) { mine_a *= rs; mine_b *= rs; }
+                        float got = __shfl_xor_sync(0xffffffffu, odd ? mine_a : mine_b, 1);
+                        float g = odd ? got : mine_a;
+                        float u = odd ? mine_b : got;
+                        int m = mb + j + (odd ? 1 : 0);
+                        if (m < p.M) out[(size_t)(j + (odd ? 1 : 0)) * p.ldo] = __float2bfloat16_rn(gelu_tanh_f(g) * u);
+                    }
                 } else {
                     // GEMM_OUT_SWIGLU: even rows hold W1 (gate), odd rows W3 (up) of channel n/2.
                     // Lanes 2i and 2i+1 swap one value per token pair; the even lane finishes

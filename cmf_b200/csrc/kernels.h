@@ -10,11 +10,11 @@
 namespace cmfc {
 
 // ---------------- dequant GEMM (gemm_dequant.cu) ----------------
-enum GemmMode : int { GEMM_OUT_F32 = 0, GEMM_OUT_BF16 = 1, GEMM_OUT_SWIGLU = 2 };
+enum GemmMode : int { GEMM_OUT_F32 = 0, GEMM_OUT_BF16 = 1, GEMM_OUT_SWIGLU = 2, GEMM_OUT_GEGLU = 3 };
 
 struct GemmParams {
     int M, N, K;             // tokens, weight rows, reduction
-    void* out;               // [M, ldo] f32 or bf16; SWIGLU writes [M, N/2] bf16
+    void* out;               // [M, ldo] f32 or bf16; SWIGLU / GEGLU write [M, N/2] bf16
     int ldo;
     int mode;
     const float* row_scale;  // q8 only: [N]
@@ -167,5 +167,26 @@ void launch_split_f32(const float* x, size_t n, __half* hi, __half* lo, cudaStre
 // group-normalized f32 output (no split): y = ((x - mean) * inv) as f32 * w + b, optional SiLU
 int launch_gn_apply_f32(const float* x, size_t pixels, int c, int groups, const double* stats, const float* w,
                         const float* b, int silu, float* y, cudaStream_t s);
+
+
+// ---------------- Gemma-2 prompt encoder (gemma_kernels.cu) ----------------
+// out[r, :] = (q8[r, :] * scale[r]) * emb_scale over gathered embedding rows
+void launch_embed_q8(const int8_t* q, const float* scale, int rows, int cols, float emb_scale, float* out, cudaStream_t s);
+void launch_scale_f32(float* x, size_t n, float sc, cudaStream_t s);
+// Activations of the encoder's GEMMs are split rows: [2n, K] bf16 with hi = bf16(v) in rows [0, n) and
+// lo = bf16(v - hi) in rows [n, 2n); a GEMM output [2n, N] f32 is consumed as the sum of its halves.
+// qkv [2n, pitch]: halves summed into rows [0, n); the first heads_qk heads get half-split RoPE in f32
+void launch_rope_half(float* qkv, int n, int heads_qk, int heads_all, int pitch, int hd, const float* cos_t,
+                      const float* sin_t, cudaStream_t s);
+// h[r] += rms(src[r] + src[n + r]) * w_res (src may be null), then, if w_next: rms(h) * w_next as split rows
+// and / or f32.  w_res / w_next hold 1 + weight.
+void launch_gemma_residual_norm(float* h, const float* src, int n, int cols, const float* w_res, const float* w_next,
+                                double eps, __nv_bfloat16* out_split, float* out_f32, cudaStream_t s);
+// gu [2n, 2 * inter] (gate / up interleaved by column) -> gelu_tanh(g) * u as split rows [2n, inter]
+void launch_geglu_split(const float* gu, int n, int inter, __nv_bfloat16* act, cudaStream_t s);
+// causal GQA attention with logit soft-capping over rows [0, n) of qkv [., (nh + 2 nkv) * hd] f32 -> split rows
+// out [2n, nh * hd]
+int launch_attn_causal_f32(const float* qkv, int n, int nh, int nkv, int hd, float scale, float softcap,
+                           __nv_bfloat16* out, cudaStream_t s);
 
 }  // namespace cmfc

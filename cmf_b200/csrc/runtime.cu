@@ -368,6 +368,7 @@ static float half_to_float_host(uint16_t h) {
     memcpy(&f, &bits, 4);
     return f;
 }
+float half_bits_to_float(uint16_t h) { return half_to_float_host(h); }
 
 static int finish_gemm_maps(DevWeight* w) {
     if (w->dtype == DT_F32) return OK;

@@ -49,6 +49,7 @@ int model_open(const char* path, Model** out);
 void model_close(Model* m);
 uint64_t hash64(const uint8_t* p, size_t n);
 size_t payload_nbytes(int dtype, size_t rows, size_t cols);
+float half_bits_to_float(uint16_t h);  // IEEE binary16 bit pattern -> f32 (host)
 
 // ---- a weight resident on the device, in the planes the kernels read ----
 struct DevWeight {

@@ -180,3 +180,62 @@ def write_vae_model(path, cfg, seed=0):
     w.write(tmp, hash_tensors=False)
     os.replace(tmp, path)
     return path
+
+
+# ---------------------------------------------------------------------------------------------
+# Synthetic Gemma-2 prompt encoder (te.* names of crates/cortiq-engine/src/textenc.rs:172-216;
+# packing rules of crates/cortiq-cli/src/imagepack.rs:129-152: embedding q8_row, *_proj weights
+# at the chosen level, norms f32).
+GEMMA2_2B = dict(hidden_size=2304, num_hidden_layers=26, num_attention_heads=8, num_key_value_heads=4, head_dim=256,
+                 intermediate_size=9216, vocab_size=256000, query_pre_attn_scalar=256, attn_logit_softcapping=50.0,
+                 rope_theta=10000.0, rms_norm_eps=1e-6, sliding_window=4096)
+TINY_GEMMA = dict(hidden_size=256, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                  intermediate_size=1024, vocab_size=512, query_pre_attn_scalar=64, attn_logit_softcapping=50.0,
+                  rope_theta=10000.0, rms_norm_eps=1e-6, sliding_window=4096)
+
+
+def gemma_tensor_list(cfg, level):
+    """[(name, dtype id, shape, kind)]; kind 'w' projection ~N(0, std), 'e' embedding, 'n' norm weight."""
+    hs, nh, nkv, hd = cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    inter = cfg["intermediate_size"]
+    out = [("te.embed_tokens.weight", DT_Q8_ROW, (cfg["vocab_size"], hs), "e")]
+    for l in range(cfg["num_hidden_layers"]):
+        p = f"te.layers.{l}"
+        out += [(p + ".input_layernorm.weight", DT_F32, (hs,), "n"),
+                (p + ".self_attn.q_proj.weight", level, (nh * hd, hs), "w"),
+                (p + ".self_attn.k_proj.weight", level, (nkv * hd, hs), "w"),
+                (p + ".self_attn.v_proj.weight", level, (nkv * hd, hs), "w"),
+                (p + ".self_attn.o_proj.weight", level, (hs, nh * hd), "w"),
+                (p + ".post_attention_layernorm.weight", DT_F32, (hs,), "n"),
+                (p + ".pre_feedforward_layernorm.weight", DT_F32, (hs,), "n"),
+                (p + ".mlp.gate_proj.weight", level, (inter, hs), "w"),
+                (p + ".mlp.up_proj.weight", level, (inter, hs), "w"),
+                (p + ".mlp.down_proj.weight", level, (hs, inter), "w"),
+                (p + ".post_feedforward_layernorm.weight", DT_F32, (hs,), "n")]
+    out.append(("te.norm.weight", DT_F32, (hs,), "n"))
+    return out
+
+
+def add_gemma(writer, cfg, level="q4t", seed=0, std=0.02):
+    """Append te.* tensors (random-init, quantized on the device) and te.config_json."""
+    lvl = CODECS[level]
+    for i, (name, dt, shape, kind) in enumerate(gemma_tensor_list(cfg, lvl)):
+        if kind == "n":
+            rng = np.random.default_rng(seed * 7907 + i)
+            writer.add_f32(name, (0.1 * rng.standard_normal(shape)).astype(np.float32))
+            continue
+        s = std if kind == "w" else 1.0 / np.sqrt(cfg["hidden_size"])
+        writer.add(name, dt, shape, gpu.encode_random(dt, seed * 100019 + i + 1, float(s), shape[0], shape[1]))
+    writer.add_json("te.config_json", {k: cfg[k] for k in (
+        "hidden_size", "num_hidden_layers", "num_attention_heads", "num_key_value_heads", "head_dim", "intermediate_size",
+        "vocab_size", "query_pre_attn_scalar", "attn_logit_softcapping", "rope_theta", "rms_norm_eps", "sliding_window")})
+
+
+def write_gemma_model(path, cfg, level="q4t", seed=0):
+    w = CmfWriter(arch={"arch_name": "gemma2-encoder-synth", "hidden_size": cfg["hidden_size"],
+                        "num_layers": cfg["num_hidden_layers"], "vocab_size": cfg["vocab_size"]}, quant_type="mixed")
+    add_gemma(w, cfg, level, seed)
+    tmp = path + f".tmp{os.getpid()}"
+    w.write(tmp, hash_tensors=False)
+    os.replace(tmp, path)
+    return path

@@ -46,6 +46,7 @@ extern "C" {
 typedef struct cmfc_model cmfc_model;     /* an opened, memory-mapped .cmf container */
 typedef struct cmfc_nextdit cmfc_nextdit; /* a NextDiT bound to a model, weights resident */
 typedef struct cmfc_vae cmfc_vae;         /* a VAE decoder bound to a model, weights resident */
+typedef struct cmfc_gemma cmfc_gemma;     /* a Gemma-2 prompt encoder bound to a model, weights resident */
 
 /* Thread-local message of the last failing call on this thread
  * (style of crates/cortiq-ffi/include/cortiq.h:5-7, cortiq_last_error). */
@@ -166,6 +167,21 @@ int cmfc_denoise_begin(cmfc_nextdit* d, const float* latents, size_t batch, size
                        size_t cap_n, const float* cap_u, size_t cap_u_n, uint32_t steps, float guidance_scale);
 int cmfc_denoise_step(cmfc_nextdit* d, uint32_t i);
 int cmfc_denoise_end(cmfc_nextdit* d, float* latents);
+
+/* ---- Gemma-2 prompt encoder (crates/cortiq-engine/src/textenc.rs): token ids -> hidden states.
+ * Projections are the container's quantized tensors (q8_row / q4_tiled / q4tp) through the dequant
+ * GEMM with bf16 activations; norms in f64 statistics, RoPE, soft-capped causal attention and the
+ * residual stream in f32. ---- */
+
+/* GemmaEncoder::from_cmf (textenc.rs:172-216): reads te.config_json and the te.* tensors */
+int cmfc_gemma_create(cmfc_model* m, cmfc_gemma** out);
+void cmfc_gemma_destroy(cmfc_gemma* g);
+/* hidden_size, num_hidden_layers, nh, nkv, head_dim, intermediate_size, vocab, sliding_window */
+int cmfc_gemma_dims(const cmfc_gemma* g, uint32_t dims[8]);
+/* GemmaEncoder::encode (textenc.rs:222-336).  final_out: null, or [n, hidden] final-normed states;
+ * streams_out: null, or [(layers + 1), n, hidden], the residual stream entering every layer and,
+ * last, the pre-final-norm stream (keep_layer_inputs).  n must be below the sliding window. */
+int cmfc_gemma_encode(cmfc_gemma* g, const uint32_t* ids, size_t n, float* final_out, float* streams_out);
 
 /* ---- VAE decoder (crates/cortiq-engine/src/vae.rs): latents [latent_channels, h, w] at model
  * scale -> RGB [3, s*h, s*w] in [-1, 1], s = 2^(up blocks with an upsampler), 8 for FLUX.

@@ -65,8 +65,9 @@ def load_for_oracle(path, cache=True):
             dt, shape, nb = m.info(i)
             name = m.name(i)
             raw = np.array(m.tensor_bytes(i), copy=True)
-            if name == "dit.config_json":
-                cfg = json.loads(raw.tobytes().decode())
+            if name.endswith(".config_json"):
+                if name == "dit.config_json" or cfg is None:
+                    cfg = json.loads(raw.tobytes().decode())
             elif dt == 0:
                 out[name] = raw.view(np.float32).reshape(shape)
             elif dt in (3, 11, 15):
