@@ -214,6 +214,41 @@ def vae_leg(args, lh, lw, peaks, cpu=True):
     return out
 
 
+def encoder_leg(args, cpu=True, n=128):
+    """The stage before the denoiser: Gemma-2-2B prompt encoder, caption features of one prompt of
+    ``n`` tokens (synthetic q4_tiled weights of the real architecture, vocabulary cut to 4096 rows)."""
+    from cmf_b200 import GemmaEncoder, Model, gpu, synth
+    cfg = dict(synth.GEMMA2_2B, vocab_size=4096)
+    path = os.path.join(args.model_dir, "cmf_bench_gemma2_q4t.cmf")
+    if not os.path.exists(path):
+        synth.write_gemma_model(path, cfg, "q4t", 0)
+    ids = np.random.default_rng(9).integers(0, cfg["vocab_size"], n).astype(np.uint32)
+    with Model(path) as m:
+        enc = GemmaEncoder(m)
+        enc.caption_features(ids)
+        ms = gpu.bench_gemma(enc, n, iters=5)
+        t0 = time.time()
+        for _ in range(5):
+            feats = enc.caption_features(ids)
+        e2e_ms = (time.time() - t0) / 5 * 1e3
+        enc.close()
+    out = {"workload": f"Gemma-2-2B encoder (25 of 26 layers: hidden_states[-2]), q4_tiled projections, {n} tokens",
+           "ms": ms, "prompts_per_s": 1e3 / ms,
+           "e2e": {"ms": e2e_ms, "prompts_per_s": 1e3 / e2e_ms, "h2d_bytes": int(ids.nbytes + n * 2304 + 4 * n),
+                   "d2h_bytes": int(feats.nbytes), "call": "cmf_b200.GemmaEncoder(model).caption_features(ids)"}}
+    if cpu:
+        from oracle import gemma as og
+        from tests.modelfile import load_for_oracle
+        t, _ = load_for_oracle(path, cache=False)
+        t0 = time.time()
+        og.GemmaOracle(t, cfg).encode(ids, keep_layer_inputs=False)
+        dt = time.time() - t0
+        out["cpu_baseline"] = {"prompts_per_s": 1.0 / dt, "kind": "port", "cores": os.cpu_count(),
+                               "sample": f"oracle encode of the same {n} tokens, all 26 layers, numpy f32 matmuls over "
+                                         f"exactly dequantized weights ({dt:.2f} s)"}
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -366,6 +401,11 @@ def main():
                 line["vae_decode"] = vae_leg(args, LH, LW, peaks, cpu=not args.no_cpu_baseline)
             except Exception as e:  # a secondary figure: never hide the headline line
                 line["vae_decode"] = {"failed": repr(e)}
+        if world == 1 and not args.no_vae:
+            try:
+                line["prompt_encode"] = encoder_leg(args, cpu=not args.no_cpu_baseline)
+            except Exception as e:
+                line["prompt_encode"] = {"failed": repr(e)}
         if args.codec in ("q4t", "q4tp"):
             # dram__bytes_read.sum + dram__bytes_write.sum of one captured launch of this kernel, the
             # gate/up GEMM of a block (N=18432, K=2304, M=8704, SwiGLU epilogue; algorithmic 224 MB):

@@ -72,6 +72,8 @@ SYMBOLS = {
     "cmfc_gemma_create": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
     "cmfc_gemma_destroy": (None, [C.c_void_p]),
     "cmfc_gemma_dims": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint32)]),
+    "cmfc_gemma_caption_features": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "cmfc_bench_gemma": (C.c_int, [C.c_void_p, C.c_size_t, C.c_int, C.POINTER(C.c_float)]),
     "cmfc_gemma_encode": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]),
     "cmfc_denoise": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p, C.c_size_t,
                                C.c_void_p, C.c_size_t, C.c_uint32, C.c_float]),

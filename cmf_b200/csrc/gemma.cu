@@ -172,8 +172,12 @@ int embed_rows(Context* c, cmfc_gemma* g, const uint32_t* ids, int n, float* h) 
     return fail(ERR_UNSUPPORTED, "te.embed_tokens.weight: expected q8_row, f32 or f16");
 }
 
-// streams: null, or device [(nl + 1), n, hidden]; final_out: null, or device [n, hidden]
-int encode_device(Context* c, cmfc_gemma* g, const uint32_t* ids, int n, float* d_streams, float* d_final) {
+// streams: null, or device [(nl + 1), n, hidden]; final_out: null, or device [n, hidden].
+// d_penultimate: null, or device [n, hidden] receiving the stream that enters the last layer; when
+// nothing else is asked for, the last layer is not run.
+int encode_device(Context* c, cmfc_gemma* g, const uint32_t* ids, int n, float* d_streams, float* d_final,
+                  float* d_penultimate) {
+    const int run_layers = (d_streams || d_final) ? g->nl : g->nl - 1;
     const int hs = g->hidden, nh = g->nh, nkv = g->nkv, hd = g->hd;
     const int qkv_cols = (nh + 2 * nkv) * hd;
     CMFC_TRY(ensure_rope(c, g, n));
@@ -198,8 +202,10 @@ int encode_device(Context* c, cmfc_gemma* g, const uint32_t* ids, int n, float* 
         launch_gemma_residual_norm(h, nullptr, n, hs, nullptr, g->layers[0].input_norm, g->eps, xn, nullptr, s);
         c->launches++;
     }
-    for (int l = 0; l < g->nl; ++l) {
+    for (int l = 0; l < run_layers; ++l) {
         const GemmaLayer& L = g->layers[l];
+        if (d_penultimate && l == g->nl - 1)
+            CMFC_CUDA(cudaMemcpyAsync(d_penultimate, h, (size_t)n * hs * 4, cudaMemcpyDeviceToDevice, s));
         if (d_streams)
             CMFC_CUDA(cudaMemcpyAsync(d_streams + (size_t)l * n * hs, h, (size_t)n * hs * 4, cudaMemcpyDeviceToDevice, s));
         {
@@ -236,6 +242,8 @@ int encode_device(Context* c, cmfc_gemma* g, const uint32_t* ids, int n, float* 
             c->launches++;
         }
     }
+    if (d_penultimate && run_layers == g->nl - 1)
+        CMFC_CUDA(cudaMemcpyAsync(d_penultimate, h, (size_t)n * hs * 4, cudaMemcpyDeviceToDevice, s));
     if (d_streams)
         CMFC_CUDA(cudaMemcpyAsync(d_streams + (size_t)g->nl * n * hs, h, (size_t)n * hs * 4, cudaMemcpyDeviceToDevice, s));
     if (d_final) {
@@ -348,9 +356,48 @@ extern "C" int cmfc_gemma_encode(cmfc_gemma* g, const uint32_t* ids, size_t n, f
     DevBuf &bs = c->buf("te.streams"), &bf = c->buf("te.final");
     if (streams_out) CMFC_TRY(bs.ensure((size_t)(g->nl + 1) * per * 4));
     if (final_out) CMFC_TRY(bf.ensure(per * 4));
-    CMFC_TRY(encode_device(c, g, ids, (int)n, streams_out ? bs.as<float>() : nullptr, final_out ? bf.as<float>() : nullptr));
+    CMFC_TRY(encode_device(c, g, ids, (int)n, streams_out ? bs.as<float>() : nullptr, final_out ? bf.as<float>() : nullptr,
+                           nullptr));
     if (streams_out)
         CMFC_CUDA(cudaMemcpyAsync(streams_out, bs.p, (size_t)(g->nl + 1) * per * 4, cudaMemcpyDeviceToHost, c->stream));
     if (final_out) CMFC_CUDA(cudaMemcpyAsync(final_out, bf.p, per * 4, cudaMemcpyDeviceToHost, c->stream));
     return check_status(c, "gemma_encode");
+}
+
+extern "C" int cmfc_gemma_caption_features(cmfc_gemma* g, const uint32_t* ids, size_t n, float* out) {
+    NEED(g && ids && out && n > 0, "gemma_caption_features: null argument or empty prompt");
+    if ((int64_t)n >= (int64_t)g->window)
+        return fail(ERR_SHAPE, "gemma_caption_features: prompt of " + std::to_string(n) +
+                                   " tokens exceeds the sliding window " + std::to_string(g->window));
+    NEED_CTX();
+    const size_t per = n * (size_t)g->hidden;
+    DevBuf& bp = c->buf("te.penult");
+    CMFC_TRY(bp.ensure(per * 4));
+    CMFC_TRY(encode_device(c, g, ids, (int)n, nullptr, nullptr, bp.as<float>()));
+    CMFC_CUDA(cudaMemcpyAsync(out, bp.p, per * 4, cudaMemcpyDeviceToHost, c->stream));
+    return check_status(c, "gemma_caption_features");
+}
+
+// instrumentation: device time of caption_features for a synthetic prompt of n tokens (CUDA events)
+extern "C" int cmfc_bench_gemma(cmfc_gemma* g, size_t n, int iters, float* ms_per_prompt) {
+    NEED(g && ms_per_prompt && n > 0 && iters > 0 && (int64_t)n < (int64_t)g->window, "bench_gemma: bad argument");
+    NEED_CTX();
+    std::vector<uint32_t> ids(n);
+    for (size_t i = 0; i < n; ++i) ids[i] = (uint32_t)((i * 2654435761u) % (uint32_t)g->vocab);
+    DevBuf& bp = c->buf("te.penult");
+    CMFC_TRY(bp.ensure(n * (size_t)g->hidden * 4));
+    CMFC_TRY(encode_device(c, g, ids.data(), (int)n, nullptr, nullptr, bp.as<float>()));
+    cudaEvent_t e0, e1;
+    CMFC_CUDA(cudaEventCreate(&e0));
+    CMFC_CUDA(cudaEventCreate(&e1));
+    CMFC_CUDA(cudaEventRecord(e0, c->stream));
+    for (int i = 0; i < iters; ++i) CMFC_TRY(encode_device(c, g, ids.data(), (int)n, nullptr, nullptr, bp.as<float>()));
+    CMFC_CUDA(cudaEventRecord(e1, c->stream));
+    CMFC_CUDA(cudaEventSynchronize(e1));
+    float ms = 0;
+    CMFC_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    *ms_per_prompt = ms / iters;
+    return check_status(c, "bench_gemma");
 }

@@ -240,6 +240,12 @@ def bench_vae_decode(vae, h, w, iters=3):
     return float(ms.value)
 
 
+def bench_gemma(enc, n, iters=5):
+    ms = C.c_float()
+    check(lib().cmfc_bench_gemma(enc.handle, n, iters, C.byref(ms)))
+    return float(ms.value)
+
+
 def bench_conv(ic, oc, h, w, k=3, a_planes=1, iters=5):
     ms = C.c_float()
     check(lib().cmfc_bench_conv(ic, oc, h, w, k, a_planes, iters, C.byref(ms)))

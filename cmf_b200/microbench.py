@@ -7,6 +7,7 @@ library).  Used for the per-kernel roofline tables and as the small cases for pr
     python -m cmf_b200.microbench sweep          # the op-level dequant-GEMM sweep of the baseline config
     python -m cmf_b200.microbench conv --ic 128 --oc 128 --h 1024 --w 1024
     python -m cmf_b200.microbench vae --latent 128   # whole FLUX-VAE decode with per-stage times
+    python -m cmf_b200.microbench gemma --n 128 --codec q4t   # Gemma-2-2B prompt encode with per-stage times
 """
 import argparse
 import json
@@ -95,9 +96,33 @@ def vae_decode(latent, iters):
             "tflops": fl / (ms * 1e-3) / 1e12, "stages": spans}
 
 
+def gemma_encode(n, codec, iters):
+    from .synth import GEMMA2_2B, write_gemma_model
+    from .textenc import GemmaEncoder
+    cfg = dict(GEMMA2_2B, vocab_size=4096)   # the forward touches n rows of the table; 4096 keep the file small
+    path = os.path.join(tempfile.gettempdir(), f"cmf_microbench_te_{os.getpid()}.cmf")
+    write_gemma_model(path, cfg, codec, 0)
+    try:
+        with Model(path) as m:
+            enc = GemmaEncoder(m)
+            ms = gpu.bench_gemma(enc, n, iters)
+            gpu.profile_enable(True)
+            gpu.bench_gemma(enc, n, 1)
+            spans = gpu.profile_read()
+            gpu.profile_enable(False)
+            enc.close()
+    finally:
+        os.remove(path)
+    hs, inter, nh, nkv, hd, nl = 2304, 9216, 8, 4, 256, 26
+    params = (nh + 2 * nkv) * hd * hs + hs * nh * hd + 3 * inter * hs
+    fl = 2.0 * n * params * (nl - 1)
+    return {"kernel": "gemma_caption_features", "tokens": n, "codec": codec, "ms": ms, "gemm_flops": fl,
+            "weights_bytes": params * (nl - 1) * {"q8": 1.0, "q4t": 0.5625, "q4tp": 0.5195}[codec], "stages": spans}
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attention", "rowops", "sweep", "conv", "vae"])
+    ap.add_argument("what", choices=["gemm", "attention", "rowops", "sweep", "conv", "vae", "gemma"])
     ap.add_argument("--codec", default="q4t", choices=["q8", "q4t", "q4tp"])
     ap.add_argument("--N", type=int, default=2304)
     ap.add_argument("--K", type=int, default=2304)
@@ -134,6 +159,8 @@ def main():
         print(json.dumps(conv(a.ic, a.oc, a.h, a.w, a.k, a.planes, a.iters)))
     elif a.what == "vae":
         print(json.dumps(vae_decode(a.latent, a.iters)))
+    elif a.what == "gemma":
+        print(json.dumps(gemma_encode(a.n if a.n != 4352 else 128, a.codec, a.iters)))
     else:
         for codec in ("q8", "q4t", "q4tp"):
             for K, N in ((2304, 2304), (2304, 6912), (2304, 9216), (9216, 2304)):

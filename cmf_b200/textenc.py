@@ -40,5 +40,7 @@ class GemmaEncoder:
     def caption_features(self, ids):
         """The features the denoiser is conditioned on: hidden_states[-2], the stream entering the
         last layer (crates/cortiq-engine/src/imagegen.rs:127-131)."""
-        _, streams = self.encode(ids, keep_layer_inputs=True)
-        return streams[-2]
+        ids = np.ascontiguousarray(ids, dtype=np.uint32)
+        out = np.empty((int(ids.size), self.hidden), np.float32)
+        check(lib().cmfc_gemma_caption_features(self.handle, ids.ctypes.data, int(ids.size), out.ctypes.data))
+        return out

@@ -182,6 +182,9 @@ int cmfc_gemma_dims(const cmfc_gemma* g, uint32_t dims[8]);
  * streams_out: null, or [(layers + 1), n, hidden], the residual stream entering every layer and,
  * last, the pre-final-norm stream (keep_layer_inputs).  n must be below the sliding window. */
 int cmfc_gemma_encode(cmfc_gemma* g, const uint32_t* ids, size_t n, float* final_out, float* streams_out);
+/* What encode_prompt hands to the denoiser (crates/cortiq-engine/src/imagegen.rs:116-139):
+ * hidden_states[-2], the stream entering the last layer, [n, hidden].  The last layer is not run. */
+int cmfc_gemma_caption_features(cmfc_gemma* g, const uint32_t* ids, size_t n, float* out);
 
 /* ---- VAE decoder (crates/cortiq-engine/src/vae.rs): latents [latent_channels, h, w] at model
  * scale -> RGB [3, s*h, s*w] in [-1, 1], s = 2^(up blocks with an upsampler), 8 for FLUX.
@@ -250,6 +253,8 @@ int cmfc_bench_attention(size_t nh, size_t nkv, size_t hd, size_t n, size_t nseg
  * launch.  kind: 0 modulated RMSNorm, 1 gated residual, 2 gated residual + next modulated norm
  * (one pass), 3 qk-norm + RoPE + head packing. */
 int cmfc_bench_rowop(int kind, size_t rows, size_t cols, int iters, float* ms_per_launch, double* bytes_per_launch);
+/* Time cmfc_gemma_caption_features on a synthetic prompt of n tokens (device work only). */
+int cmfc_bench_gemma(cmfc_gemma* g, size_t n, int iters, float* ms_per_prompt);
 /* Time whole VAE decodes of a synthetic latent [latent_channels, h, w] resident on the device. */
 int cmfc_bench_vae_decode(cmfc_vae* v, size_t h, size_t w, int iters, float* ms_per_decode);
 /* Time the implicit-GEMM convolution ic -> oc (k x k, k 1 or 3) over an h x w image of synthetic
