@@ -13,3 +13,4 @@ from .container import CmfWriter, Model  # noqa: F401
 from .dit import NextDit, GenParams, denoise  # noqa: F401
 from .vae import VaeDecoder  # noqa: F401
 from .textenc import GemmaEncoder  # noqa: F401
+from .imagegen import Pipeline, generate  # noqa: F401

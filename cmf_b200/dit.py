@@ -16,10 +16,13 @@ def _f32(a):
 
 @dataclass
 class GenParams:
-    """imagegen.rs:41-55 (fields the denoiser uses)."""
+    """imagegen.rs:22-55 (the fields this backend uses)."""
     steps: int = 30
     guidance_scale: float = 4.0
     seed: int = 42
+    height: int = 512
+    width: int = 512
+    max_tokens: int = 256
 
 
 class NextDit:

@@ -280,3 +280,13 @@ def test_bad_arguments_never_reach_a_launch():
     assert L.cmfc_payload_nbytes(11, 4, 64) == 4 * 2 * 18
     assert L.cmfc_payload_nbytes(15, 7, 64) == 7 * 2 * 16 + 7 * 4 + 7 * 2
     assert b"null" in L.cmfc_last_error()
+
+
+def test_product_gauss_latent_equals_oracle():
+    """cmf_b200.imagegen.gauss_latent (vectorised) against the scalar restatement of
+    crates/cortiq-engine/src/imagegen.rs:75-108."""
+    from cmf_b200.imagegen import gauss_latent, to_rgb01
+    from oracle.nextdit import gauss_latent as ref
+    for n, seed in ((1, 0), (7, 42), (1001, 1), (4096, 2 ** 63 + 5)):
+        assert np.array_equal(gauss_latent(n, seed), ref(n, seed))
+    assert to_rgb01(np.array([-3.0, -1.0, 0.0, 1.0, 3.0], np.float32)).tolist() == [0.0, 0.0, 0.5, 1.0, 1.0]
