@@ -184,7 +184,18 @@ __global__ void __launch_bounds__(256) attn_causal_f32_kernel(const float* __res
         float acc[GQ];
 #pragma unroll
         for (int r = 0; r < GQ; ++r) acc[r] = 0.0f;
-        for (int j = 0; j <= last; ++j) {
+        // keys in ascending order (the reference's summation order); eight V loads in flight
+        int j = 0;
+        for (; j + 8 <= last + 1; j += 8) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = vbase[(size_t)(j + u) * pitch + d];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+#pragma unroll
+                for (int r = 0; r < GQ; ++r) acc[r] = __fadd_rn(acc[r], __fmul_rn(S[r * s_pitch + j + u], v[u]));
+        }
+        for (; j <= last; ++j) {
             const float v = vbase[(size_t)j * pitch + d];
 #pragma unroll
             for (int r = 0; r < GQ; ++r) acc[r] = __fadd_rn(acc[r], __fmul_rn(S[r * s_pitch + j], v));
