@@ -303,13 +303,10 @@ gemm_dequant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
             const int n = n0 + row;
             float rs = 1.0f;
             if (WKIND == 0) rs = p.row_scale[n];
-#pragma unroll 1
-            for (int c = ehalf * (TT / 64); c < (ehalf + 1) * (TT / 64); ++c) {
-                uint32_t v[32];
-                tmem_ld_x32(tmem + lane_addr + buf * TT + c * 32, v);
-                tc_wait_ld();
+            // one 32-token chunk of this thread's output channel
+            auto emit = [&](const uint32_t (&v)[32], int c) {
                 const int mb = m0 + c * 32;
-                if (mb >= p.M) break;
+                if (mb >= p.M) return;
                 if (p.mode == GEMM_OUT_F32) {
                     float* out = reinterpret_cast<float*>(p.out) + (size_t)mb * p.ldo + n;
 #pragma unroll
@@ -351,10 +348,29 @@ gemm_dequant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
                         if (m < p.M) out[(size_t)(j + (odd ? 1 : 0)) * p.ldo] = __float2bfloat16_rn(silu_f(g) * u);
                     }
                 }
+            };
+            // The TMEM load of a chunk is issued before the previous chunk is converted and stored,
+            // and the accumulator is handed back to the MMA warp as soon as the last load has landed
+            // (the stores of the last chunk overlap the next tile's first MMAs).
+            const int c0 = ehalf * (TT / 64);
+            const uint32_t t0 = tmem + lane_addr + buf * TT + c0 * 32;
+            uint32_t va[32], vb[32];
+            tmem_ld_x32(t0, va);
+#pragma unroll 1
+            for (int i = 0; i < TT / 64; i += 2) {
+                tc_wait_ld();
+                tmem_ld_x32(t0 + (i + 1) * 32, vb);
+                emit(va, c0 + i);
+                tc_wait_ld();
+                if (i + 2 < TT / 64) {
+                    tmem_ld_x32(t0 + (i + 2) * 32, va);
+                } else {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bars->acc_empty[buf]);
+                }
+                emit(vb, c0 + i + 1);
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bars->acc_empty[buf]);
         }
     }
 
