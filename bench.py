@@ -275,6 +275,8 @@ def main():
     from cmf_b200 import GenParams, Model, NextDit, denoise, gpu, synth
 
     if world > 1:
+        # stdout carries exactly one JSON line: NCCL's own banner / debug lines go to stderr
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     gpu.set_current_device(local)
