@@ -387,6 +387,7 @@ gemm_dequant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
 }  // namespace
 
 int gemm_smem_bytes() { return SMEM_BYTES; }
+int gemm_tile_tokens() { return TT; }
 
 int launch_gemm_dequant(int wkind, const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUtensorMap& tm_s,
                         const GemmParams& p, int num_sms, cudaStream_t stream) {

@@ -22,6 +22,7 @@ struct GemmParams {
 };
 
 int gemm_smem_bytes();
+int gemm_tile_tokens();  // rows of the activation TMA box
 int launch_gemm_dequant(int wkind, const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUtensorMap& tm_s,
                         const GemmParams& p, int num_sms, cudaStream_t stream);
 

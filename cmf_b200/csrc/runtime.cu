@@ -574,7 +574,7 @@ int dev_gemm(Context* c, DevWeight* w, const __nv_bfloat16* x, int M, void* out,
         return fail(ERR_SHAPE, "dequant GEMM needs rows % 128 == 0 and cols % 64 == 0 (got " + std::to_string(w->rows) +
                                    " x " + std::to_string(w->cols) + ")");
     CUtensorMap tm_x;
-    CMFC_TRY(make_tensor_map_2d(&tm_x, x, 2, (uint64_t)M, (uint64_t)w->cols, (uint64_t)w->cols * 2, 256, 64, 3));
+    CMFC_TRY(make_tensor_map_2d(&tm_x, x, 2, (uint64_t)M, (uint64_t)w->cols, (uint64_t)w->cols * 2, gemm_tile_tokens(), 64, 3));
     GemmParams p;
     p.M = M; p.N = w->rows; p.K = w->cols;
     p.out = out; p.ldo = ldo; p.mode = mode;
