@@ -36,6 +36,7 @@ struct AttnBars {
     uint64_t k_full[KV_STAGES], k_empty[KV_STAGES];
     uint64_t v_full[KV_STAGES], v_empty[KV_STAGES];
     uint64_t s_full[2], p_full[2], r_full[2];
+    uint64_t stagger;  // tile A's softmax warps are half way through their first key tile
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
@@ -84,6 +85,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             mbar_init(&bars->s_full[t], 1);
             mbar_init(&bars->p_full[t], 4);
             mbar_init(&bars->r_full[t], 1);
+            if (t == 0) mbar_init(&bars->stagger, 4);
         }
         bars->abort_flag = 0;
         mbar_fence_init();
@@ -148,11 +150,18 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             if (ok) ok = mbar_wait(&bars->k_full[0], 0, abort_flag, 14);
             if (ok) {
                 tc_fence_after();
+                // The two query tiles share the special-function unit (softmax) and the tensor pipe
+                // (MMAs).  Started together they stay in phase, each waiting on the unit the other one
+                // holds; tile B starts once tile A is half way through its first softmax, and the
+                // offset persists (a tile's MMAs then run while the other tile exponentiates).
                 issue_s(0, 0);
                 tc_commit(&bars->s_full[0]);
-                issue_s(1, 0);
-                tc_commit(&bars->s_full[1]);
-                tc_commit(&bars->k_empty[0]);
+                ok = mbar_wait(&bars->stagger, 0, abort_flag, 18);
+                if (ok) {
+                    issue_s(1, 0);
+                    tc_commit(&bars->s_full[1]);
+                    tc_commit(&bars->k_empty[0]);
+                }
             }
             for (int j = 0; ok && j < nk; ++j) {
                 const int s = j % KV_STAGES;
@@ -245,6 +254,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     pk[i >> 1] = pack_bf16(e0, e1);
                 }
                 tmem_st_x16(tmem + lane_addr + s_col(t) + ch * 16, pk);
+                if (ch == 1 && t == 0 && j == 0) {
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bars->stagger);
+                }
             }
             tc_wait_st();
             l_run += sum;
