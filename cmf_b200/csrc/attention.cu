@@ -16,6 +16,13 @@
 //                  it by more than 8 (in log2 units), so P stays below 2^8 and the O row in TMEM
 //                  is multiplied by exp2(m_old - m_new) on the few tiles where that happens
 // While the softmax warps of tile A work, the tensor core runs tile B, and vice versa.
+//
+// TMEM plan for head_dim <= 96 ("split" plan): S of tile A / B at columns 0 / 128, ONE P buffer
+// shared by both tiles at 256 (64 columns of packed bf16), O of tile A / B at 320 / 416.  P no
+// longer overwrites S, so S(j+1) of a tile is issued as soon as its softmax warps have pulled
+// S(j) into registers and is ready long before they need it: a tile never waits for the tensor
+// pipe, only for the shared P buffer, which the other tile's P V frees half a period earlier.
+// head_dim 128 does not fit that plan (O needs 2 x 128 columns) and keeps P over S.
 #include "common.cuh"
 #include "kernels.h"
 
@@ -26,9 +33,10 @@ constexpr int QT = 128;   // query rows per tile (UMMA M)
 constexpr int KT = 128;   // keys per tile (UMMA N for S, K extent for P V)
 constexpr int KV_STAGES = 2;
 constexpr int ATTN_THREADS = 32 * 10;  // TMA, MMA, 4 softmax warps for tile A, 4 for tile B
-// TMEM columns: S (and P over it) of tile A / B at 0 / 128, the O accumulator at 256 / 384
 __host__ __device__ constexpr int s_col(int t) { return t * 128; }
-__host__ __device__ constexpr int r_col(int t) { return 256 + t * 128; }
+template <int HD> __host__ __device__ constexpr bool split_plan() { return HD <= 96; }
+template <int HD> __host__ __device__ constexpr int p_col(int t) { return split_plan<HD>() ? 256 : s_col(t); }
+template <int HD> __host__ __device__ constexpr int r_col(int t) { return split_plan<HD>() ? 320 + t * 96 : 256 + t * 128; }
 constexpr int ATTN_TMEM_COLS = 512;
 
 struct AttnBars {
@@ -37,6 +45,8 @@ struct AttnBars {
     uint64_t v_full[KV_STAGES], v_empty[KV_STAGES];
     uint64_t s_full[2], p_full[2], r_full[2];
     uint64_t stagger;  // tile A's softmax warps are half way through their first key tile
+    uint64_t s_read[2];  // split plan: the tile's softmax warps hold S(j) in registers
+    uint64_t p_free[2];  // split plan: the shared P buffer may be written by tile t
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
@@ -86,6 +96,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             mbar_init(&bars->p_full[t], 4);
             mbar_init(&bars->r_full[t], 1);
             if (t == 0) mbar_init(&bars->stagger, 4);
+            mbar_init(&bars->s_read[t], 4);
+            mbar_init(&bars->p_free[t], 1);
         }
         bars->abort_flag = 0;
         mbar_fence_init();
@@ -143,7 +155,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 const uint32_t va = smem_u32(v_smem + s * L::V_TILE);
 #pragma unroll
                 for (int kk = 0; kk < KT / 16; ++kk)
-                    mma_ts(tmem + r_col(t), tmem + s_col(t) + kk * 8,
+                    mma_ts(tmem + r_col<HD>(t), tmem + p_col<HD>(t) + kk * 8,
                            smem_desc_kmajor(va + (kk >> 2) * HD * 128 + (kk & 3) * 32, 128), IDESC_R, !first || kk != 0);
             };
             bool ok = mbar_wait(&bars->q_full, 0, abort_flag, 13);
@@ -169,22 +181,44 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 const bool more = j + 1 < nk;
                 const int s1 = (j + 1) % KV_STAGES;
                 const uint32_t ph1 = ((j + 1) / KV_STAGES) & 1u;
-                if (!mbar_wait(&bars->v_full[s], ph, abort_flag, 15)) { ok = false; break; }
-                if (more && !mbar_wait(&bars->k_full[s1], ph1, abort_flag, 16)) { ok = false; break; }
-                for (int t = 0; t < 2; ++t) {
-                    // P_t(j) is in TMEM (and the O row was rescaled if its reference maximum moved)
-                    if (!mbar_wait(&bars->p_full[t], jp, abort_flag, 17)) { ok = false; break; }
-                    tc_fence_after();
-                    issue_r(t, s, j == 0);
-                    tc_commit(&bars->r_full[t]);
-                    if (more) {
-                        issue_s(t, s1);
-                        tc_commit(&bars->s_full[t]);
+                if constexpr (split_plan<HD>()) {
+                    if (more && !mbar_wait(&bars->k_full[s1], ph1, abort_flag, 16)) { ok = false; break; }
+                    for (int t = 0; t < 2 && ok; ++t) {
+                        if (more) {
+                            // the tile's softmax warps hold S(j) in registers: its columns are free
+                            if (!mbar_wait(&bars->s_read[t], jp, abort_flag, 22)) { ok = false; break; }
+                            tc_fence_after();
+                            issue_s(t, s1);
+                            tc_commit(&bars->s_full[t]);
+                            if (t == 1) tc_commit(&bars->k_empty[s1]);
+                        }
+                        if (t == 0 && !mbar_wait(&bars->v_full[s], ph, abort_flag, 15)) { ok = false; break; }
+                        if (!mbar_wait(&bars->p_full[t], jp, abort_flag, 17)) { ok = false; break; }
+                        tc_fence_after();
+                        issue_r(t, s, j == 0);
+                        tc_commit(&bars->r_full[t]);
+                        tc_commit(&bars->p_free[t ^ 1]);  // the other tile may now write the shared P buffer
                     }
+                    if (!ok) break;
+                    tc_commit(&bars->v_empty[s]);
+                } else {
+                    if (!mbar_wait(&bars->v_full[s], ph, abort_flag, 15)) { ok = false; break; }
+                    if (more && !mbar_wait(&bars->k_full[s1], ph1, abort_flag, 16)) { ok = false; break; }
+                    for (int t = 0; t < 2; ++t) {
+                        // P_t(j) is in TMEM (and the O row was rescaled if its reference maximum moved)
+                        if (!mbar_wait(&bars->p_full[t], jp, abort_flag, 17)) { ok = false; break; }
+                        tc_fence_after();
+                        issue_r(t, s, j == 0);
+                        tc_commit(&bars->r_full[t]);
+                        if (more) {
+                            issue_s(t, s1);
+                            tc_commit(&bars->s_full[t]);
+                        }
+                    }
+                    if (!ok) break;
+                    tc_commit(&bars->v_empty[s]);
+                    if (more) tc_commit(&bars->k_empty[s1]);
                 }
-                if (!ok) break;
-                tc_commit(&bars->v_empty[s]);
-                if (more) tc_commit(&bars->k_empty[s1]);
             }
         }
     } else {
@@ -204,22 +238,33 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #pragma unroll
             for (int ch = 0; ch < 4; ++ch) tmem_ld_x32(tmem + lane_addr + s_col(t) + ch * 32, v[ch]);
             tc_wait_ld();
+            if constexpr (split_plan<HD>()) {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars->s_read[t]);
+            }
             const int valid = seg_len - j * KT;  // keys of this tile inside the segment
-            float mx = -INFINITY;
+            // row maximum: eight independent chains (a single running maximum is a 128-deep
+            // dependency chain on the critical path between S and P)
+            float mxs[8];
+#pragma unroll
+            for (int a = 0; a < 8; ++a) mxs[a] = -INFINITY;
             if (valid >= KT) {
 #pragma unroll
                 for (int ch = 0; ch < 4; ++ch)
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[ch][i]));
+                    for (int i = 0; i < 32; ++i) mxs[i & 7] = fmaxf(mxs[i & 7], __uint_as_float(v[ch][i]));
             } else {
 #pragma unroll
                 for (int ch = 0; ch < 4; ++ch)
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         if (ch * 32 + i >= valid) v[ch][i] = 0xff800000u;  // -inf: exp2 gives 0
-                        mx = fmaxf(mx, __uint_as_float(v[ch][i]));
+                        mxs[i & 7] = fmaxf(mxs[i & 7], __uint_as_float(v[ch][i]));
                     }
             }
+            const float mx = fmaxf(fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])),
+                                   fmaxf(fmaxf(mxs[4], mxs[5]), fmaxf(mxs[6], mxs[7])));
             const float m_cand = mx * c;
             const bool moved = m_cand > m_ref + 8.0f;  // always true on the first tile
             if (__any_sync(0xffffffffu, moved)) {
@@ -230,37 +275,53 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 if (moved) m_ref = m_cand;
                 l_run *= alpha;
                 if (j > 0) {
+                    if constexpr (split_plan<HD>()) {
+                        // S(j) was issued before P V of tile j-1: wait for that MMA before touching O
+                        if (!mbar_wait(&bars->r_full[t], (j - 1) & 1u, abort_flag, 23)) { ok = false; break; }
+                        tc_fence_after();
+                    }
                     // rare path, small chunks: the score row stays live in registers meanwhile
 #pragma unroll 1
                     for (int ch = 0; ch < HD / 8; ++ch) {
                         uint32_t o[8];
-                        tmem_ld_x8(tmem + lane_addr + r_col(t) + ch * 8, o);
+                        tmem_ld_x8(tmem + lane_addr + r_col<HD>(t) + ch * 8, o);
                         tc_wait_ld();
 #pragma unroll
                         for (int i = 0; i < 8; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                        tmem_st_x8(tmem + lane_addr + r_col(t) + ch * 8, o);
+                        tmem_st_x8(tmem + lane_addr + r_col<HD>(t) + ch * 8, o);
                     }
                 }
             }
-            float sum = 0.0f;
+            float sums[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            uint32_t pk[4][16];
 #pragma unroll
             for (int ch = 0; ch < 4; ++ch) {
-                uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
                     const float e0 = ex2_approx(fmaf(__uint_as_float(v[ch][i]), c, -m_ref));
                     const float e1 = ex2_approx(fmaf(__uint_as_float(v[ch][i + 1]), c, -m_ref));
-                    sum += e0 + e1;
-                    pk[i >> 1] = pack_bf16(e0, e1);
+                    sums[(i >> 1) & 3] += e0 + e1;
+                    pk[ch][i >> 1] = pack_bf16(e0, e1);
                 }
-                tmem_st_x16(tmem + lane_addr + s_col(t) + ch * 16, pk);
+                if constexpr (!split_plan<HD>()) tmem_st_x16(tmem + lane_addr + p_col<HD>(t) + ch * 16, pk[ch]);
                 if (ch == 1 && t == 0 && j == 0) {
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&bars->stagger);
                 }
             }
+            if constexpr (split_plan<HD>()) {
+                // The P buffer is shared by the two tiles: it is held only from here to the end of
+                // this tile's P V.  Tile A needs P V of tile B's previous key tile done, tile B needs
+                // P V of tile A's current one (the MMA warp serves A before B in every step).
+                if (t == 1 || j > 0) {
+                    if (!mbar_wait<40>(&bars->p_free[t], (t == 1 ? j : j - 1) & 1u, abort_flag, 24)) { ok = false; break; }
+                    tc_fence_after();
+                }
+#pragma unroll
+                for (int ch = 0; ch < 4; ++ch) tmem_st_x16(tmem + lane_addr + p_col<HD>(t) + ch * 16, pk[ch]);
+            }
             tc_wait_st();
-            l_run += sum;
+            l_run += (sums[0] + sums[1]) + (sums[2] + sums[3]);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars->p_full[t]);
@@ -273,7 +334,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #pragma unroll
             for (int ch = 0; ch < HD / 32; ++ch) {
                 uint32_t o[32];
-                tmem_ld_x32(tmem + lane_addr + r_col(t) + ch * 32, o);
+                tmem_ld_x32(tmem + lane_addr + r_col<HD>(t) + ch * 32, o);
                 tc_wait_ld();
                 if (qrow < seg_len) {
 #pragma unroll
