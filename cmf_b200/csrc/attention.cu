@@ -32,7 +32,7 @@ namespace {
 constexpr int QT = 128;   // query rows per tile (UMMA M)
 constexpr int KT = 128;   // keys per tile (UMMA N for S, K extent for P V)
 constexpr int KV_STAGES = 2;
-constexpr int ATTN_THREADS = 32 * 10;  // TMA, MMA, 4 softmax warps for tile A, 4 for tile B
+constexpr int ATTN_THREADS = 32 * 11;  // TMA, MMA (tile A), 4 + 4 softmax warps, MMA (tile B, split plan)
 __host__ __device__ constexpr int s_col(int t) { return t * 128; }
 template <int HD> __host__ __device__ constexpr bool split_plan() { return HD <= 96; }
 template <int HD> __host__ __device__ constexpr int p_col(int t) { return split_plan<HD>() ? 256 : s_col(t); }
@@ -87,9 +87,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         mbar_init(&bars->q_full, 1);
         for (int s = 0; s < KV_STAGES; ++s) {
             mbar_init(&bars->k_full[s], 1);
-            mbar_init(&bars->k_empty[s], 1);
+            // split plan: each tile has its own MMA warp, and both must be done with a stage
+            mbar_init(&bars->k_empty[s], split_plan<HD>() ? 2 : 1);
             mbar_init(&bars->v_full[s], 1);
-            mbar_init(&bars->v_empty[s], 1);
+            mbar_init(&bars->v_empty[s], split_plan<HD>() ? 2 : 1);
         }
         for (int t = 0; t < 2; ++t) {
             mbar_init(&bars->s_full[t], 1);
@@ -137,9 +138,13 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                                 kvh * HD);
             }
         }
-    } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
-        if (elect_one()) {
+    } else if (warp == 1 || warp == 10) {
+        // ---------------- MMA issuer(s) ----------------
+        // split plan: warp 1 issues for tile A, warp 10 for tile B, each in its tile's own order
+        // (a single thread walking a fixed order over both tiles stalls one tile on the other).
+        if (warp == 10 && !split_plan<HD>()) {
+            // nothing to do
+        } else if (elect_one()) {
             constexpr uint32_t IDESC_S = idesc_bf16_f32(QT, KT);
             constexpr uint32_t IDESC_R = idesc_bf16_f32(QT, HD);
             auto issue_s = [&](int t, int s) {
@@ -160,48 +165,56 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             };
             bool ok = mbar_wait(&bars->q_full, 0, abort_flag, 13);
             if (ok) ok = mbar_wait(&bars->k_full[0], 0, abort_flag, 14);
-            if (ok) {
-                tc_fence_after();
-                // The two query tiles share the special-function unit (softmax) and the tensor pipe
-                // (MMAs).  Started together they stay in phase, each waiting on the unit the other one
-                // holds; tile B starts once tile A is half way through its first softmax, and the
-                // offset persists (a tile's MMAs then run while the other tile exponentiates).
-                issue_s(0, 0);
-                tc_commit(&bars->s_full[0]);
-                ok = mbar_wait(&bars->stagger, 0, abort_flag, 18);
+            if constexpr (split_plan<HD>()) {
+                const int t = warp == 1 ? 0 : 1;
+                // The two query tiles share the special-function unit (softmax) and the tensor pipe.
+                // Started together they stay in phase, each waiting on the unit the other one holds;
+                // tile B starts once tile A is half way through its first softmax.
+                if (ok && t == 1) ok = mbar_wait(&bars->stagger, 0, abort_flag, 18);
                 if (ok) {
-                    issue_s(1, 0);
-                    tc_commit(&bars->s_full[1]);
+                    tc_fence_after();
+                    issue_s(t, 0);
+                    tc_commit(&bars->s_full[t]);
                     tc_commit(&bars->k_empty[0]);
                 }
-            }
-            for (int j = 0; ok && j < nk; ++j) {
-                const int s = j % KV_STAGES;
-                const uint32_t ph = (j / KV_STAGES) & 1u, jp = j & 1u;
-                const bool more = j + 1 < nk;
-                const int s1 = (j + 1) % KV_STAGES;
-                const uint32_t ph1 = ((j + 1) / KV_STAGES) & 1u;
-                if constexpr (split_plan<HD>()) {
-                    if (more && !mbar_wait(&bars->k_full[s1], ph1, abort_flag, 16)) { ok = false; break; }
-                    for (int t = 0; t < 2 && ok; ++t) {
-                        if (more) {
-                            // the tile's softmax warps hold S(j) in registers: its columns are free
-                            if (!mbar_wait(&bars->s_read[t], jp, abort_flag, 22)) { ok = false; break; }
-                            tc_fence_after();
-                            issue_s(t, s1);
-                            tc_commit(&bars->s_full[t]);
-                            if (t == 1) tc_commit(&bars->k_empty[s1]);
-                        }
-                        if (t == 0 && !mbar_wait(&bars->v_full[s], ph, abort_flag, 15)) { ok = false; break; }
-                        if (!mbar_wait(&bars->p_full[t], jp, abort_flag, 17)) { ok = false; break; }
+                for (int j = 0; ok && j < nk; ++j) {
+                    const int s = j % KV_STAGES, s1 = (j + 1) % KV_STAGES;
+                    const uint32_t jp = j & 1u;
+                    if (j + 1 < nk) {
+                        // S(j + 1) as soon as the tile's softmax warps hold S(j) in registers
+                        if (!mbar_wait(&bars->k_full[s1], ((j + 1) / KV_STAGES) & 1u, abort_flag, 16)) { ok = false; break; }
+                        if (!mbar_wait(&bars->s_read[t], jp, abort_flag, 22)) { ok = false; break; }
                         tc_fence_after();
-                        issue_r(t, s, j == 0);
-                        tc_commit(&bars->r_full[t]);
-                        tc_commit(&bars->p_free[t ^ 1]);  // the other tile may now write the shared P buffer
+                        issue_s(t, s1);
+                        tc_commit(&bars->s_full[t]);
+                        tc_commit(&bars->k_empty[s1]);
                     }
-                    if (!ok) break;
+                    if (!mbar_wait(&bars->v_full[s], (j / KV_STAGES) & 1u, abort_flag, 15)) { ok = false; break; }
+                    if (!mbar_wait(&bars->p_full[t], jp, abort_flag, 17)) { ok = false; break; }
+                    tc_fence_after();
+                    issue_r(t, s, j == 0);
+                    tc_commit(&bars->r_full[t]);
+                    tc_commit(&bars->p_free[t ^ 1]);  // the other tile may now write the shared P buffer
                     tc_commit(&bars->v_empty[s]);
-                } else {
+                }
+            } else {
+                if (ok) {
+                    tc_fence_after();
+                    issue_s(0, 0);
+                    tc_commit(&bars->s_full[0]);
+                    ok = mbar_wait(&bars->stagger, 0, abort_flag, 18);
+                    if (ok) {
+                        issue_s(1, 0);
+                        tc_commit(&bars->s_full[1]);
+                        tc_commit(&bars->k_empty[0]);
+                    }
+                }
+                for (int j = 0; ok && j < nk; ++j) {
+                    const int s = j % KV_STAGES;
+                    const uint32_t ph = (j / KV_STAGES) & 1u, jp = j & 1u;
+                    const bool more = j + 1 < nk;
+                    const int s1 = (j + 1) % KV_STAGES;
+                    const uint32_t ph1 = ((j + 1) / KV_STAGES) & 1u;
                     if (!mbar_wait(&bars->v_full[s], ph, abort_flag, 15)) { ok = false; break; }
                     if (more && !mbar_wait(&bars->k_full[s1], ph1, abort_flag, 16)) { ok = false; break; }
                     for (int t = 0; t < 2; ++t) {

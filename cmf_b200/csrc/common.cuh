@@ -90,6 +90,20 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Non-blocking probe of a phase.
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // Same, but the hardware may park the thread for up to ``hint_ns`` while the phase is pending,
 // so a waiting warp does not compete for issue slots with the warps doing the work.
 __device__ __forceinline__ bool mbar_try_parked(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
