@@ -180,6 +180,8 @@ extern "C" int cmfc_ffn(cmfc_model* m, int64_t w1, int64_t w3, int64_t w2, const
 extern "C" int cmfc_dit_attention(const float* qh, const float* kh, const float* vh, size_t nh, size_t nkv, size_t n,
                                   size_t hd, float scale, float* out) {
     NEED(qh && kh && vh && out && n > 0 && nh > 0 && nkv > 0, "dit_attention: null argument or empty input");
+    // the VAE's attention block: one head as wide as the channel count (vae.rs:438)
+    if (hd > 128 && nh == 1 && nkv == 1) return attention_single_head_wide(qh, kh, vh, n, hd, scale, out);
     NEED_CTX();
     std::vector<int> segs{(int)n};
     SegTable st;

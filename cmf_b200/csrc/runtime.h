@@ -139,6 +139,9 @@ int dev_block(Context* c, const BlockWeights& bw, const BlockMod& mod, float* x,
               const BlockChain* chain = nullptr);
 
 bool row_cols_supported(int cols);
+// single-head attention with a head wider than the flash kernel's 128 (host f32 in / out), vae.cu
+int attention_single_head_wide(const float* q, const float* k, const float* v, size_t n, size_t c_dim, float scale,
+                               float* out);
 void launch_gemv_silu2(const GemvParams& p, float* y_silu, cudaStream_t s);
 
 struct SpanGuard {

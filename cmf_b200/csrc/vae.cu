@@ -664,3 +664,65 @@ extern "C" int cmfc_bench_conv(size_t ic, size_t oc, size_t h, size_t w, size_t 
     *ms_per_launch = ms / iters;
     return check_status(c, "bench_conv");
 }
+
+// gpu::dit_attention as the VAE's attention block calls it (crates/cortiq-engine/src/vae.rs:438:
+// one head, head dimension = channels = 512): host q, k, v [n, c] f32 -> out [n, c] f32 through the
+// split-f16 GEMMs and the materialised score plane.  Reached from cmfc_dit_attention when the head
+// dimension exceeds the flash kernel's 128.
+namespace cmfc {
+int attention_single_head_wide(const float* q, const float* k, const float* v, size_t n, size_t c_dim, float scale,
+                               float* out) {
+    Context* c = ctx();
+    if (!c) return last_error().empty() ? fail(ERR_CUDA, "no CUDA device") : ERR_CUDA;
+    if (c_dim % 32 || c_dim > 4096) return fail(ERR_SHAPE, "dit_attention: a head wider than 128 must be a multiple of 32 (<= 4096)");
+    if (n > 51200) return fail(ERR_SHAPE, "dit_attention: wide-head path holds a score row in shared memory (n <= 51200)");
+    const int ch = (int)c_dim, nn = (int)n, n_pad = round_up(nn, 32);
+    const size_t tok = n * c_dim;
+    DevBuf &bin = c->buf("wa.in"), &bq = c->buf("wa.q"), &bk = c->buf("wa.k"), &bvt = c->buf("wa.vt"), &bs = c->buf("wa.s"),
+           &bp = c->buf("wa.p"), &bo = c->buf("wa.o");
+    CMFC_TRY(bin.ensure(3 * tok * 4));
+    CMFC_TRY(bq.ensure(tok * 4));
+    CMFC_TRY(bk.ensure(tok * 4));
+    CMFC_TRY(bvt.ensure((size_t)ch * n_pad * 4));
+    CMFC_TRY(bs.ensure(n * (size_t)n_pad * 4));
+    CMFC_TRY(bp.ensure(n * (size_t)n_pad * 4));
+    CMFC_TRY(bo.ensure(tok * 4));
+    float* d_in = bin.as<float>();
+    CMFC_CUDA(cudaMemcpyAsync(d_in, q, tok * 4, cudaMemcpyHostToDevice, c->stream));
+    CMFC_CUDA(cudaMemcpyAsync(d_in + tok, k, tok * 4, cudaMemcpyHostToDevice, c->stream));
+    CMFC_CUDA(cudaMemcpyAsync(d_in + 2 * tok, v, tok * 4, cudaMemcpyHostToDevice, c->stream));
+    const Planes qp{bq.as<__half>(), bq.as<__half>() + tok}, kp{bk.as<__half>(), bk.as<__half>() + tok};
+    const Planes vt{bvt.as<__half>(), bvt.as<__half>() + (size_t)ch * n_pad};
+    const Planes pr{bp.as<__half>(), bp.as<__half>() + n * (size_t)n_pad};
+    launch_split_f32(d_in, tok, qp.hi, qp.lo, c->stream);
+    launch_split_f32(d_in + tok, tok, kp.hi, kp.lo, c->stream);
+    // V [n, c] -> V^T split planes [c, n_pad]: the transpose kernel reads "NCHW" = [rows, pixels]
+    CMFC_CUDA(cudaMemsetAsync(bvt.p, 0, (size_t)ch * n_pad * 4, c->stream));
+    {
+        DevBuf& bt = c->buf("wa.t");
+        CMFC_TRY(bt.ensure(tok * 4));
+        launch_nhwc_to_nchw(d_in + 2 * tok, n, ch, bt.as<float>(), c->stream);   // [n, c] -> [c, n]
+        if (n_pad == nn) {
+            launch_split_f32(bt.as<float>(), tok, vt.hi, vt.lo, c->stream);
+        } else {
+            for (int r = 0; r < ch; ++r)  // ragged pitch: row by row (small c)
+                launch_split_f32(bt.as<float>() + (size_t)r * n, n, vt.hi + (size_t)r * n_pad, vt.lo + (size_t)r * n_pad, c->stream);
+        }
+    }
+    CMFC_CUDA(cudaGetLastError());
+    c->launches += 4;
+    CUtensorMap tk_hi, tk_lo, tv_hi, tv_lo;
+    CMFC_TRY(make_tensor_map_2d(&tk_hi, kp.hi, 2, n, ch, (uint64_t)ch * 2, 128, 32, 2));
+    CMFC_TRY(make_tensor_map_2d(&tk_lo, kp.lo, 2, n, ch, (uint64_t)ch * 2, 128, 32, 2));
+    ConvOut os; os.f32 = bs.as<float>(); os.pitch = n_pad; os.scale = scale;
+    CMFC_TRY(run_gemm(c, tk_hi, tk_lo, 2, nn, ch, 1, nullptr, qp, 2, ch, ch, nn, 1, os));
+    CMFC_TRY(launch_softmax_rows_split(bs.as<float>(), n, nn, (size_t)n_pad, pr.hi, pr.lo, (size_t)n_pad, c->stream));
+    c->launches++;
+    CMFC_TRY(make_tensor_map_2d(&tv_hi, vt.hi, 2, ch, n, (uint64_t)n_pad * 2, 128, 32, 2));
+    CMFC_TRY(make_tensor_map_2d(&tv_lo, vt.lo, 2, ch, n, (uint64_t)n_pad * 2, 128, 32, 2));
+    ConvOut oo; oo.f32 = bo.as<float>();
+    CMFC_TRY(run_gemm(c, tv_hi, tv_lo, 2, ch, n_pad, 1, nullptr, pr, 2, nn, n_pad, nn, 1, oo));
+    CMFC_CUDA(cudaMemcpyAsync(out, bo.p, tok * 4, cudaMemcpyDeviceToHost, c->stream));
+    return check_status(c, "dit_attention");
+}
+}  // namespace cmfc

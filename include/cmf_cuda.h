@@ -96,7 +96,10 @@ int cmfc_ffn(cmfc_model* m, int64_t w1, int64_t w3, int64_t w2, const float* xs,
              size_t inter, float* out);
 
 /* gpu.rs:2332 dit_attention: q [nh][n][hd], k and v [nkv][n][hd] head-major f32 (q NOT yet
- * scaled), out [n][nh*hd]; bidirectional softmax attention, GQA */
+ * scaled), out [n][nh*hd]; bidirectional softmax attention, GQA.  hd <= 128 (a multiple of 32)
+ * runs the flash kernel with bf16 operands; a single head wider than that (nh = nkv = 1, hd a
+ * multiple of 32: the VAE's attention block, vae.rs:438) runs in f32 semantics through the
+ * split-f16 GEMMs and a materialised score plane. */
 int cmfc_dit_attention(const float* qh, const float* kh, const float* vh, size_t nh, size_t nkv, size_t n,
                        size_t hd, float scale, float* out);
 

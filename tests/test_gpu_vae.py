@@ -153,3 +153,21 @@ def test_decoder_1024_runs_and_is_deterministic(tmp_path):
     assert np.array_equal(a, b)
     assert not np.array_equal(a[:, :256, :256], c[:, :256, :256])
     assert a.std() > 1e-3
+
+
+@pytest.mark.parametrize("n,c", [(256, 512), (100, 512), (64, 160)])
+def test_dit_attention_single_wide_head(n, c):
+    """gpu::dit_attention as the VAE's attention block calls it (crates/cortiq-engine/src/vae.rs:438):
+    one head whose dimension is the channel count, f32 in and out."""
+    from cmf_b200 import gpu
+    rng = np.random.default_rng(n + c)
+    q, k, v = (rng.standard_normal((n, c)).astype(np.float32) for _ in range(3))
+    scale = 1.0 / np.sqrt(np.float32(c))
+    out = np.empty((n, c), np.float32)
+    assert gpu.dit_attention(q, k, v, 1, 1, n, c, float(scale), out)
+    s = (q.astype(np.float64) @ k.astype(np.float64).T) * float(scale)
+    s -= s.max(axis=1, keepdims=True)
+    p = np.exp(s)
+    p /= p.sum(axis=1, keepdims=True)
+    want = (p @ v.astype(np.float64)).astype(np.float32)
+    assert rel_l2(out, want) < 2e-5
