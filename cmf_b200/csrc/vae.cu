@@ -675,7 +675,7 @@ int attention_single_head_wide(const float* q, const float* k, const float* v, s
     Context* c = ctx();
     if (!c) return last_error().empty() ? fail(ERR_CUDA, "no CUDA device") : ERR_CUDA;
     if (c_dim % 32 || c_dim > 4096) return fail(ERR_SHAPE, "dit_attention: a head wider than 128 must be a multiple of 32 (<= 4096)");
-    if (n > 51200) return fail(ERR_SHAPE, "dit_attention: wide-head path holds a score row in shared memory (n <= 51200)");
+    if (n > 131072) return fail(ERR_SHAPE, "dit_attention: wide-head path materialises n x n scores (n <= 131072)");
     const int ch = (int)c_dim, nn = (int)n, n_pad = round_up(nn, 32);
     const size_t tok = n * c_dim;
     DevBuf &bin = c->buf("wa.in"), &bq = c->buf("wa.q"), &bk = c->buf("wa.k"), &bvt = c->buf("wa.vt"), &bs = c->buf("wa.s"),

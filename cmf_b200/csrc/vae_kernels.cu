@@ -255,6 +255,40 @@ __global__ void __launch_bounds__(256) softmax_rows_split_kernel(const float* __
     }
 }
 
+// The same for rows longer than shared memory holds: three passes over the row in global memory
+// (the row stays in L2 between them).
+__global__ void __launch_bounds__(256) softmax_rows_split_long_kernel(const float* __restrict__ scores, int cols, size_t ld,
+                                                                      __half* __restrict__ hi, __half* __restrict__ lo,
+                                                                      size_t ldp) {
+    __shared__ float red[8];
+    const float* src = scores + (size_t)blockIdx.x * ld;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float mx = -3.4028234663852886e38f;
+    for (int i = threadIdx.x; i < cols; i += 256) mx = fmaxf(mx, src[i]);
+    for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) red[warp] = mx;
+    __syncthreads();
+    mx = red[0];
+    for (int i = 1; i < 8; ++i) mx = fmaxf(mx, red[i]);
+    __syncthreads();
+    float den = 0.0f;
+    for (int i = threadIdx.x; i < cols; i += 256) den += expf(src[i] - mx);
+    den = warp_sum(den);
+    if (lane == 0) red[warp] = den;
+    __syncthreads();
+    den = 0.0f;
+    for (int i = 0; i < 8; ++i) den += red[i];
+    const float inv = 1.0f / den;
+    __half* dh = hi + (size_t)blockIdx.x * ldp;
+    __half* dl = lo + (size_t)blockIdx.x * ldp;
+    for (int i = threadIdx.x; i < cols; i += 256) {
+        const float p = expf(src[i] - mx) * inv;
+        const __half h = __float2half_rn(p);
+        dh[i] = h;
+        dl[i] = __float2half_rn(p - __half2float(h));
+    }
+}
+
 bool gn_channels_ok(int c) { return c >= 32 && c <= 1024 && (c & (c - 1)) == 0; }
 
 }  // namespace
@@ -330,8 +364,12 @@ void launch_conv_weight_split(const float* w, int oc, int ic, int taps, int ic_p
 int launch_softmax_rows_split(const float* scores, size_t rows, int cols, size_t ld, __half* hi, __half* lo, size_t ldp,
                               cudaStream_t s) {
     const size_t smem = (size_t)cols * 4;
-    if (smem > 200 * 1024) return fail(ERR_UNSUPPORTED, "softmax: a score row must fit 200 KiB of shared memory");
     if (rows > 0x7fffffffu) return fail(ERR_SHAPE, "softmax: too many rows");
+    if (smem > 200 * 1024) {
+        softmax_rows_split_long_kernel<<<(unsigned)rows, 256, 0, s>>>(scores, cols, ld, hi, lo, ldp);
+        CMFC_CUDA(cudaGetLastError());
+        return OK;
+    }
     static bool configured[64] = {false};
     int dev = 0;
     CMFC_CUDA(cudaGetDevice(&dev));
