@@ -34,7 +34,7 @@ METRIC = "nextdit_denoise_steps_per_s_1024sq_q4t"
 UNIT = "steps/s"
 H = W = 128                  # latent of a 1024x1024 image
 CAP_N = 256
-STEP_TFLOP = 45.9            # algorithmic FLOPs of one CFG-pair step at 1024^2
+STEP_TFLOP = 45.9            # algorithmic FLOPs of one CFG-pair step at 1024^2 (26 joint + 4 refiner blocks)
 
 
 def env_int(name, default):

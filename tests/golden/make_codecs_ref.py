@@ -23,7 +23,9 @@ def inputs():
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit(__doc__)
+    ref = sys.argv[1]
     sys.path.insert(0, os.path.join(ref, "converter"))
     sys.path.insert(0, os.path.join(ref, "python"))
     import cmf_reader

@@ -60,7 +60,9 @@ def run_reference(ref, cfg, t, ids):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit(__doc__)
+    root = sys.argv[1]
     sys.path.insert(0, os.path.join(root, "python"))
     import gemma_ref as ref
     for name, (cfg, wseed, ids) in CASES.items():

@@ -74,7 +74,9 @@ def inputs(cfg, seed, H, W, cap_n):
 
 
 def main():
-    refroot = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit(__doc__)
+    refroot = sys.argv[1]
     sys.path.insert(0, os.path.join(refroot, "python"))
     import nextdit_ref as ref
     for name, (cfg, wseed, jit, std, iseed, H, W, cap_n, t) in CASES.items():
