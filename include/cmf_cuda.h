@@ -1,6 +1,6 @@
 /*
  * libcmf_cuda -- B200 (sm_100a) compute backend for the NextDiT denoiser path of the CMF
- * engine.  Plain C ABI: pointers and sizes only.  Every entry returns 0 on success or a
+ * engine (and the prompt encoder and VAE decoder on either side of it).  Plain C ABI: pointers and sizes only.  Every entry returns 0 on success or a
  * negative status; cmfc_last_error() gives the thread's last message.  Nothing throws or
  * aborts across this boundary, and nothing falls back to the CPU: an entry either ran on the
  * device or failed with a status.
@@ -9,7 +9,9 @@
  * repository; `gpu.rs` is crates/cortiq-engine/src/gpu.rs, the engine's backend facade).
  *
  * Host pointers are borrowed for the duration of the call.  Weight bytes are copied to the
- * device once per (model, directory index) and owned by the library until cmfc_model_close.
+ * device once per (model, directory index) and owned by the library until cmfc_model_close;
+ * a cmfc_nextdit / cmfc_gemma / cmfc_vae handle refers to those copies and must be destroyed
+ * before its model is closed.
  * Calls on one device context are serialized by the caller (the engine drives a denoise from
  * one thread); the current device is selected per thread with cmfc_set_device.
  */
