@@ -1,7 +1,8 @@
 /*
  * libcmf_cuda -- B200 (sm_100a) compute backend for the NextDiT denoiser path of the CMF
- * engine (and the prompt encoder and VAE decoder on either side of it).  Plain C ABI: pointers and sizes only.  Every entry returns 0 on success or a
- * negative status; cmfc_last_error() gives the thread's last message.  Nothing throws or
+ * engine (and the prompt encoder and VAE decoder on either side of it).  Plain C ABI: pointers
+ * and sizes only.  Every entry returns 0 on success or a negative status; cmfc_last_error()
+ * gives the thread's last message.  Nothing throws or
  * aborts across this boundary, and nothing falls back to the CPU: an entry either ran on the
  * device or failed with a status.
  *
