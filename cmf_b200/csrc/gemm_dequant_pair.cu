@@ -1,0 +1,375 @@
+// Dequant-fused GEMM on CTA PAIRS (tcgen05 cta_group::2): the two CTAs of a cluster compute one
+// tile of 256 weight rows x 256 tokens.  Same operand definition and data path as
+// gemm_dequant.cu (dequantized weights are the A operand in tensor memory, activations the B
+// operand in shared memory), with the work of a tile split as the 2-SM MMA wants it:
+//   * each CTA owns 128 of the 256 weight rows: it fetches and unpacks its own packed weight
+//     tile into its own tensor memory, and drains its own 128 x 256 accumulator;
+//   * each CTA fetches only HALF of the activation tile (128 tokens x 64 k, 16 KiB); the MMA of
+//     the pair reads both halves from the two CTAs' shared memory, so an activation byte crosses
+//     L2 -> SM once per 256 weight rows instead of once per 128, and the ring is 8 stages deep;
+//   * one thread of the even CTA issues tcgen05.mma.cta_group::2 (M = 256, N = 256, K = 16) and
+//     releases stages in both CTAs with multicast commits; the odd CTA's warps signal the even
+//     CTA's barriers (A tile ready, accumulator drained) with remote arrives.
+// Every bulk tensor load here is a plain or cta_group::2 load of this GPU's own memory, one copy per CTA.
+// Every wait is bounded; the pair leaves through a cluster barrier so that neither CTA exits
+// while the other may still touch its shared or tensor memory.
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+#include "gemm_unpack.cuh"
+#include "kernels.h"
+
+namespace cmfc {
+namespace {
+
+using namespace gemm_detail;
+namespace cg = cooperative_groups;
+
+constexpr int TW = 128;      // weight rows per CTA (the pair covers 256)
+constexpr int TT = 256;      // tokens per pair tile (UMMA N)
+constexpr int TH = TT / 2;   // tokens whose activations this CTA stages
+constexpr int BK = 64;
+constexpr int STAGES = 8;
+constexpr int ASTAGES = 8;
+static_assert(STAGES == ASTAGES, "one commit per k-block releases both rings");
+constexpr int X_STAGE = TH * BK * 2;   // 16 KiB
+constexpr int W_STAGE = TW * BK;       // 8 KiB
+constexpr int S_STAGE = 2 * TW * 4;    // 1 KiB
+constexpr int A_COL = TT;
+constexpr int TMEM_COLS = 512;
+constexpr int NUM_DQ_WARPS = 8;
+constexpr int NUM_EPI_WARPS = 8;
+constexpr int THREADS = 32 * (2 + NUM_DQ_WARPS + NUM_EPI_WARPS);
+constexpr int SMEM_BYTES = STAGES * (X_STAGE + W_STAGE + S_STAGE) + 1024 + 512;
+constexpr uint32_t PEER_MASK = 0xFEFFFFFFu;  // clears the CTA-rank bit of a shared::cluster address: the even CTA
+
+struct Bars {
+    uint64_t x_full[STAGES];    // even CTA: both activation halves have landed
+    uint64_t w_full[STAGES];    // own packed weight tile (and scales) has landed
+    uint64_t empty[STAGES];     // own packed weight stage consumed by the 8 dequant warps
+    uint64_t a_full[ASTAGES];   // even CTA: both CTAs' A tiles are in tensor memory (16 arrivals)
+    uint64_t a_empty[ASTAGES];  // the pair's MMAs of this k-block are done: A stage and activation stage free
+                                // (one multicast commit per k-block; STAGES == ASTAGES, same index)
+    uint64_t acc_full;          // own accumulator complete (multicast commit)
+    uint64_t acc_empty;         // even CTA: both accumulators drained (16 arrivals)
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+};
+
+__device__ __forceinline__ void arrive_on_even_cta(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(smem_u32(bar) & PEER_MASK) : "memory");
+}
+// activation half of this CTA; the transaction bytes are counted on the EVEN CTA's barrier
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar) & PEER_MASK), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_slot, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_slot)), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// the pair's MMA: A (this CTA's and the peer's 128 rows) from tensor memory, B halves from both
+// CTAs' shared memory at the descriptor's offset
+__device__ __forceinline__ void mma_ts_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc), "r"(0u)
+        : "memory");
+}
+// completion of the pair's MMAs issued so far -> the barrier at this offset in BOTH CTAs
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+        ::"r"(smem_u32(bar)), "h"((uint16_t)3)
+        : "memory");
+}
+
+template <int WKIND>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_dequant_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
+                         const __grid_constant__ CUtensorMap tm_s, GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* x_smem = smem;
+    uint8_t* w_smem = smem + STAGES * X_STAGE;
+    uint8_t* s_smem = w_smem + STAGES * W_STAGE;
+    Bars* bars = reinterpret_cast<Bars*>(s_smem + STAGES * S_STAGE);
+    volatile uint32_t* abort_flag = &bars->abort_flag;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int rank = (int)cluster.block_rank();   // 0: even CTA (issues the MMAs), 1: odd CTA
+    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int kblocks = p.K / BK;
+    const int tiles_m = (p.M + TT - 1) / TT;
+    const int tiles_n = p.N / (2 * TW);
+    const int tiles = tiles_m * tiles_n;
+    constexpr uint32_t W_BYTES = (WKIND == 0) ? TW * BK : TW * BK / 2;
+    constexpr uint32_t WTX_BYTES = W_BYTES + (WKIND != 0 ? S_STAGE : 0);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&bars->x_full[s], 1);
+            mbar_init(&bars->w_full[s], 1);
+            mbar_init(&bars->empty[s], NUM_DQ_WARPS);
+        }
+        for (int a = 0; a < ASTAGES; ++a) {
+            mbar_init(&bars->a_full[a], 2 * NUM_DQ_WARPS);
+            mbar_init(&bars->a_empty[a], 1);
+        }
+        mbar_init(&bars->acc_full, 1);
+        mbar_init(&bars->acc_empty, 2 * NUM_EPI_WARPS);
+        bars->abort_flag = 0;
+        mbar_fence_init();
+        tma_prefetch_desc(&tm_x);
+        tma_prefetch_desc(&tm_w);
+        if (WKIND != 0) tma_prefetch_desc(&tm_s);
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(&bars->tmem_base, TMEM_COLS);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster.sync();  // both CTAs' barriers are initialised before anyone signals across the pair
+    tc_fence_after();
+    const uint32_t tmem = bars->tmem_base;
+
+    if (warp == 0) {
+        // ---------------- TMA producer (both CTAs) ----------------
+        if (elect_one()) {
+            uint32_t it = 0;
+            for (int tile = pair; tile < tiles && !*abort_flag; tile += pairs) {
+                const int n0 = (tile % tiles_n) * (2 * TW) + rank * TW, m0 = (tile / tiles_n) * TT + rank * TH;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1u;
+                    if (!mbar_wait<200>(&bars->empty[s], ph ^ 1u, abort_flag, 1)) break;
+                    if (!mbar_wait<200>(&bars->a_empty[s], ph ^ 1u, abort_flag, 8)) break;
+                    if (rank == 0) mbar_expect_tx(&bars->x_full[s], 2 * X_STAGE);
+                    tma_load_2d_pair(x_smem + s * X_STAGE, &tm_x, &bars->x_full[s], kb * BK, m0);
+                    mbar_expect_tx(&bars->w_full[s], WTX_BYTES);
+                    if (WKIND == 0) {
+                        tma_load_2d(w_smem + s * W_STAGE, &tm_w, &bars->w_full[s], kb * BK, n0);
+                    } else {
+                        tma_load_2d(w_smem + s * W_STAGE, &tm_w, &bars->w_full[s], kb * (BK / 2), n0);
+                        tma_load_2d(s_smem + s * S_STAGE, &tm_s, &bars->w_full[s], n0, kb * 2);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer (even CTA only) ----------------
+        if (rank == 0 && elect_one()) {
+            constexpr uint32_t IDESC = idesc_bf16_f32(2 * TW, TT);
+            uint32_t it = 0, tile_i = 0;
+            for (int tile = pair; tile < tiles && !*abort_flag; tile += pairs, ++tile_i) {
+                if (!mbar_wait(&bars->acc_empty, (tile_i & 1u) ^ 1u, abort_flag, 2)) break;
+                tc_fence_after();
+                bool ok = true;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % STAGES, ai = it % ASTAGES;
+                    const uint32_t ph = (it / STAGES) & 1u, aph = (it / ASTAGES) & 1u;
+                    if (!mbar_wait(&bars->x_full[s], ph, abort_flag, 3) ||
+                        !mbar_wait(&bars->a_full[ai], aph, abort_flag, 4)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t xs = smem_u32(x_smem + s * X_STAGE);
+#pragma unroll
+                    for (int j = 0; j < BK / 16; ++j)
+                        mma_ts_pair(tmem, tmem + A_COL + ai * 32 + j * 8, smem_desc_kmajor(xs + j * 32, 128), IDESC, (kb | j) != 0);
+                    tc_commit_pair(&bars->a_empty[ai]);
+                }
+                if (!ok) break;
+                tc_commit_pair(&bars->acc_full);
+            }
+        }
+    } else if (warp < 2 + NUM_DQ_WARPS) {
+        // ---------------- dequant warps (both CTAs, own weight rows) ----------------
+        const int dq = warp - 2;
+        const int quarter = warp & 3;
+        const int half = dq >> 2;
+        const int row = quarter * 32 + lane;
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        uint32_t it = 0;
+        bool ok = true;
+        int pending = -1;
+        auto flush = [&]() {
+            if (pending >= 0) {
+                tc_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) arrive_on_even_cta(&bars->a_full[pending]);
+                pending = -1;
+            }
+        };
+        for (int tile = pair; tile < tiles && ok && !*abort_flag; tile += pairs) {
+            for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                const int s = it % STAGES, ai = it % ASTAGES;
+                const uint32_t ph = (it / STAGES) & 1u, aph = (it / ASTAGES) & 1u;
+                if (!mbar_wait<100>(&bars->w_full[s], ph, abort_flag, 5)) { ok = false; break; }
+                uint32_t a[16];
+                if (WKIND == 0) {
+                    const uint8_t* wrow = w_smem + s * W_STAGE + row * 64;
+                    const int sw = (row >> 1) & 3;
+                    uint4 v0 = lds128(wrow + (((2 * half) ^ sw) << 4));
+                    uint4 v1 = lds128(wrow + (((2 * half + 1) ^ sw) << 4));
+                    unpack_q8_word(v0.x, a[0], a[1]);   unpack_q8_word(v0.y, a[2], a[3]);
+                    unpack_q8_word(v0.z, a[4], a[5]);   unpack_q8_word(v0.w, a[6], a[7]);
+                    unpack_q8_word(v1.x, a[8], a[9]);   unpack_q8_word(v1.y, a[10], a[11]);
+                    unpack_q8_word(v1.z, a[12], a[13]); unpack_q8_word(v1.w, a[14], a[15]);
+                } else {
+                    const uint8_t* wrow = w_smem + s * W_STAGE + row * 32;
+                    const int sw = (row >> 2) & 1;
+                    uint4 v = lds128(wrow + ((half ^ sw) << 4));
+                    if (WKIND == 1) {
+                        const float sc = reinterpret_cast<const float*>(s_smem + s * S_STAGE)[half * TW + row];
+                        const Q4Scales q(sc);
+                        unpack_q4_word(v.x, q, a + 0);
+                        unpack_q4_word(v.y, q, a + 4);
+                        unpack_q4_word(v.z, q, a + 8);
+                        unpack_q4_word(v.w, q, a + 12);
+                    } else {
+                        const uint32_t sc = reinterpret_cast<const uint32_t*>(s_smem + s * S_STAGE)[half * TW + row];
+                        const uint32_t hi2 = __byte_perm(sc, sc, 0x1010), lo2 = __byte_perm(sc, sc, 0x3232);
+                        unpack_q4t_word(v.x, hi2, lo2, a + 0);
+                        unpack_q4t_word(v.y, hi2, lo2, a + 4);
+                        unpack_q4t_word(v.z, hi2, lo2, a + 8);
+                        unpack_q4t_word(v.w, hi2, lo2, a + 12);
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars->empty[s]);
+                flush();
+                if (!mbar_wait<100>(&bars->a_empty[ai], aph ^ 1u, abort_flag, 7)) { ok = false; break; }
+                tc_fence_after();
+                tmem_st_x16(tmem + lane_addr + A_COL + ai * 32 + half * 16, a);
+                pending = ai;
+            }
+        }
+        flush();
+    } else {
+        // ---------------- epilogue warps (both CTAs, own accumulator rows) ----------------
+        const int quarter = warp & 3;
+        const int ehalf = (warp - 2 - NUM_DQ_WARPS) >> 2;
+        const int row = quarter * 32 + lane;
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        uint32_t tile_i = 0;
+        for (int tile = pair; tile < tiles && !*abort_flag; tile += pairs, ++tile_i) {
+            const int n0 = (tile % tiles_n) * (2 * TW) + rank * TW, m0 = (tile / tiles_n) * TT;
+            if (!mbar_wait<80>(&bars->acc_full, tile_i & 1u, abort_flag, 6)) break;
+            tc_fence_after();
+            const int n = n0 + row;
+            float rs = 1.0f;
+            if (WKIND == 0) rs = p.row_scale[n];
+            auto emit = [&](const uint32_t (&v)[32], int c) {
+                const int mb = m0 + c * 32;
+                if (mb >= p.M) return;
+                if (p.mode == GEMM_OUT_F32) {
+                    float* out = reinterpret_cast<float*>(p.out) + (size_t)mb * p.ldo + n;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (mb + j < p.M) out[(size_t)j * p.ldo] = __uint_as_float(v[j]) * rs;
+                } else if (p.mode == GEMM_OUT_BF16) {
+                    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)mb * p.ldo + n;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (mb + j < p.M) out[(size_t)j * p.ldo] = __float2bfloat16_rn(__uint_as_float(v[j]) * rs);
+                } else {
+                    // gate / up pairs in adjacent lanes (see gemm_dequant.cu); SiLU or tanh-GELU on the gate
+                    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)mb * p.ldo + (n >> 1);
+                    const bool odd = lane & 1;
+                    const bool gelu = p.mode == GEMM_OUT_GEGLU;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) {
+                        float mine_a = __uint_as_float(v[j]), mine_b = __uint_as_float(v[j + 1]);
+                        if (WKIND == 0) { mine_a *= rs; mine_b *= rs; }
+                        float got = __shfl_xor_sync(0xffffffffu, odd ? mine_a : mine_b, 1);
+                        float g = odd ? got : mine_a;
+                        float u = odd ? mine_b : got;
+                        int m = mb + j + (odd ? 1 : 0);
+                        const float act = gelu ? gelu_tanh_f(g) : silu_f(g);
+                        if (m < p.M) out[(size_t)(j + (odd ? 1 : 0)) * p.ldo] = __float2bfloat16_rn(act * u);
+                    }
+                }
+            };
+            const int c0 = ehalf * (TT / 64);
+            const uint32_t t0 = tmem + lane_addr + c0 * 32;
+            uint32_t va[32], vb[32];
+            tmem_ld_x32(t0, va);
+#pragma unroll 1
+            for (int i = 0; i < TT / 64; i += 2) {
+                tc_wait_ld();
+                tmem_ld_x32(t0 + (i + 1) * 32, vb);
+                emit(va, c0 + i);
+                tc_wait_ld();
+                if (i + 2 < TT / 64) {
+                    tmem_ld_x32(t0 + (i + 2) * 32, va);
+                } else {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) arrive_on_even_cta(&bars->acc_empty);
+                }
+                emit(vb, c0 + i + 1);
+            }
+        }
+    }
+
+    // ---------------- common exit ----------------
+    tc_fence_before();
+    __syncthreads();
+    cluster.sync();  // the peer is done with this CTA's shared and tensor memory
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem, TMEM_COLS);
+    }
+    if (threadIdx.x == 0 && bars->abort_flag) atomicCAS(p.status, 0u, 0x400u | bars->abort_flag);
+}
+
+}  // namespace
+
+bool gemm_pair_supported(const GemmParams& p) { return p.K % BK == 0 && p.N % (2 * TW) == 0 && p.M > 0; }
+int gemm_pair_tile_tokens() { return TH; }
+
+int launch_gemm_dequant_pair(int wkind, const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUtensorMap& tm_s,
+                             const GemmParams& p, int num_sms, cudaStream_t stream) {
+    if (!gemm_pair_supported(p)) return fail(ERR_SHAPE, "pair GEMM needs K % 64 == 0 and N % 256 == 0");
+    static bool configured[3][64] = {};
+    auto kern = wkind == 0 ? gemm_dequant_pair_kernel<0> : (wkind == 1 ? gemm_dequant_pair_kernel<1> : gemm_dequant_pair_kernel<2>);
+    int dev = 0;
+    CMFC_CUDA(cudaGetDevice(&dev));
+    if (!configured[wkind][dev & 63]) {
+        CMFC_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        configured[wkind][dev & 63] = true;
+    }
+    const int tiles = ((p.M + TT - 1) / TT) * (p.N / (2 * TW));
+    int pairs = num_sms / 2;
+    if (tiles < pairs) pairs = tiles;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    CMFC_CUDA(cudaLaunchKernelEx(&cfg, kern, tm_x, tm_w, tm_s, p));
+    return OK;
+}
+
+}  // namespace cmfc

@@ -26,6 +26,14 @@ int gemm_tile_tokens();  // rows of the activation TMA box
 int launch_gemm_dequant(int wkind, const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUtensorMap& tm_s,
                         const GemmParams& p, int num_sms, cudaStream_t stream);
 
+// The same GEMM on CTA pairs (gemm_dequant_pair.cu): tiles of 256 weight rows x 256 tokens, each CTA
+// staging half of the activation tile.  Needs N % 256 == 0; tm_x must have a box of
+// gemm_pair_tile_tokens() rows.
+bool gemm_pair_supported(const GemmParams& p);
+int gemm_pair_tile_tokens();
+int launch_gemm_dequant_pair(int wkind, const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUtensorMap& tm_s,
+                             const GemmParams& p, int num_sms, cudaStream_t stream);
+
 // ---------------- flash attention (attention.cu) ----------------
 struct AttnParams {
     int nh, nkv, hd;         // hd must be a multiple of 32, <= 128

@@ -573,15 +573,23 @@ int dev_gemm(Context* c, DevWeight* w, const __nv_bfloat16* x, int M, void* out,
     if (!w->gemm_ready)
         return fail(ERR_SHAPE, "dequant GEMM needs rows % 128 == 0 and cols % 64 == 0 (got " + std::to_string(w->rows) +
                                    " x " + std::to_string(w->cols) + ")");
-    CUtensorMap tm_x;
-    CMFC_TRY(make_tensor_map_2d(&tm_x, x, 2, (uint64_t)M, (uint64_t)w->cols, (uint64_t)w->cols * 2, gemm_tile_tokens(), 64, 3));
     GemmParams p;
     p.M = M; p.N = w->rows; p.K = w->cols;
     p.out = out; p.ldo = ldo; p.mode = mode;
     p.row_scale = w->dtype == DT_Q8 ? w->scales : nullptr;
     p.status = c->status;
+    const int wkind = w->dtype == DT_Q8 ? 0 : (w->dtype == DT_Q4TP ? 1 : 2);
+    // CTA-pair kernel (2-SM MMA) whenever the weight rows tile by 256 and there is at least one
+    // tile per pair of SMs; otherwise the single-CTA kernel.  CMFC_GEMM_PAIR=0 forces the latter.
+    static const bool use_pair = [] { const char* e = getenv("CMFC_GEMM_PAIR"); return !(e && e[0] == '0'); }();
+    const long pair_tiles = (long)((M + 255) / 256) * (w->rows / 256);
+    const bool pair = use_pair && gemm_pair_supported(p) && pair_tiles >= c->num_sms / 2;
+    CUtensorMap tm_x;
+    CMFC_TRY(make_tensor_map_2d(&tm_x, x, 2, (uint64_t)M, (uint64_t)w->cols, (uint64_t)w->cols * 2,
+                                pair ? gemm_pair_tile_tokens() : gemm_tile_tokens(), 64, 3));
     c->launches++;
-    return launch_gemm_dequant(w->dtype == DT_Q8 ? 0 : (w->dtype == DT_Q4TP ? 1 : 2), tm_x, w->tm_w, w->tm_s, p, c->num_sms, c->stream);
+    if (pair) return launch_gemm_dequant_pair(wkind, tm_x, w->tm_w, w->tm_s, p, c->num_sms, c->stream);
+    return launch_gemm_dequant(wkind, tm_x, w->tm_w, w->tm_s, p, c->num_sms, c->stream);
 }
 
 // Segment table on the device: [nseg+1] token offsets, then [nseg] first V^T column of each
