@@ -385,7 +385,7 @@ def main():
             "e2e": {"value": world * P * K / e2e_s, "unit": UNIT, "h2d_bytes_per_step": h2d / K, "d2h_bytes_per_step": d2h / K,
                     "call": "cmf_b200.denoise(dit, latents, cap, cap_u, GenParams(steps=K)) with pinned host buffers"
                             + ("; + NCCL gather of final latents to rank 0" if world > 1 else "")},
-            "roofline": {"kernel": "gemm_dequant_kernel (q4 nibble planes -> bf16 in TMEM -> tcgen05.mma)",
+            "roofline": {"kernel": "gemm_dequant_pair_kernel (q4 nibble planes -> bf16 in TMEM -> tcgen05.mma.cta_group::2)",
                          "bound": "tensor", "achieved": achieved, "peak": peaks["bf16_sustained"], "unit": "TFLOP/s",
                          "frac": (achieved / peaks["bf16_sustained"]) if achieved else None,
                          "peak_source": peaks["source"] + " (sustained cuBLAS bf16)",
@@ -410,9 +410,9 @@ def main():
                 line["prompt_encode"] = {"failed": repr(e)}
         if args.codec in ("q4t", "q4tp"):
             # dram__bytes_read.sum + dram__bytes_write.sum of one captured launch of this kernel, the
-            # gate/up GEMM of a block (N=18432, K=2304, M=8704, SwiGLU epilogue; algorithmic 224 MB):
+            # gate/up GEMM of a block (N=18432, K=2304, M=8704, SwiGLU epilogue; algorithmic 224 MB; pair kernel):
             # profiles/gemm_dequant_q4t_swiglu_N18432_K2304_M8704.md
-            line["roofline"]["traffic"] = 207.2e6
+            line["roofline"]["traffic"] = 196.5e6
             line["roofline"]["traffic_launch"] = "gate/up GEMM of one block, N=18432 K=2304 M=8704"
         print(json.dumps(line), flush=True)
     dit.close()
