@@ -275,10 +275,21 @@ def main():
     from cmf_b200 import GenParams, Model, NextDit, denoise, gpu, synth
 
     if world > 1:
-        # stdout carries exactly one JSON line: NCCL's own banner / debug lines go to stderr
+        # stdout carries exactly one JSON line: while NCCL sets itself up (its version banner goes to
+        # file descriptor 1) stdout is pointed at stderr, then restored
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         torch.cuda.set_device(local)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        sys.stdout.flush()
+        saved_fd = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+            dist.barrier()          # creates the communicator now
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved_fd, 1)
+            os.close(saved_fd)
     gpu.set_current_device(local)
     cfg = synth.LUMINA2
     attn, ffn = {"q4t": ("q4t", "q4t"), "q4tp": ("q4tp", "q4tp"), "q8": ("q8", "q8"),
