@@ -581,7 +581,8 @@ int dev_gemm(Context* c, DevWeight* w, const __nv_bfloat16* x, int M, void* out,
     const int wkind = w->dtype == DT_Q8 ? 0 : (w->dtype == DT_Q4TP ? 1 : 2);
     // CTA-pair kernel (2-SM MMA) whenever the weight rows tile by 256 and there is at least one
     // tile per pair of SMs; otherwise the single-CTA kernel.  CMFC_GEMM_PAIR=0 forces the latter.
-    static const bool use_pair = [] { const char* e = getenv("CMFC_GEMM_PAIR"); return !(e && e[0] == '0'); }();
+    const char* pair_env = getenv("CMFC_GEMM_PAIR");  // read per call: tests flip it between calls
+    const bool use_pair = !(pair_env && pair_env[0] == '0');
     const long pair_tiles = (long)((M + 255) / 256) * (w->rows / 256);
     const bool pair = use_pair && gemm_pair_supported(p) && pair_tiles >= c->num_sms / 2;
     CUtensorMap tm_x;

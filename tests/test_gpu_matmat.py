@@ -132,3 +132,25 @@ def test_qkv_and_ffn(tmp_path, codecs):
     u = oc.matmat_exact(qs["w3"].dtype, qs["w3"].payload, inter, hs, x)
     want = oc.matmat_exact(qs["w2"].dtype, qs["w2"].payload, hs, inter, silu(g) * u)
     assert rel_l2(out, want) < TOL
+
+
+@pytest.mark.parametrize("dt", [oc.Q8_ROW, oc.Q4_TILED, oc.Q4TP])
+@pytest.mark.parametrize("M", [4352, 2700])
+def test_pair_kernel_equals_single_cta_kernel(tmp_path, monkeypatch, dt, M):
+    """The CTA-pair GEMM (2-SM MMA, 256 x 256 tiles) and the single-CTA GEMM (128 x 256 tiles) feed
+    the tensor core the same operands in the same k order: same bits out.  M = 2700 leaves a ragged
+    last token tile whose second half is entirely out of range."""
+    from cmf_b200 import Model, gpu
+    rng = np.random.default_rng(3)
+    K, N = 2304, 9216                                   # 36 row pairs x 11 or 17 token tiles: the pair path
+    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    x = oc.bf16_round(rng.standard_normal((M, K)).astype(np.float32))
+    path = str(tmp_path / "w.cmf")
+    single_weight_file(path, [("w", dt, w)])
+    with Model(path) as m:
+        monkeypatch.setenv("CMFC_GEMM_PAIR", "1")
+        a = _call(gpu, dt, m, m.index("w"), x, N, K)
+        monkeypatch.setenv("CMFC_GEMM_PAIR", "0")
+        b = _call(gpu, dt, m, m.index("w"), x, N, K)
+    assert np.isfinite(a).all()
+    assert np.array_equal(a, b)
