@@ -37,9 +37,10 @@ constexpr int W_STAGE = TW * BK;       // 8 KiB
 constexpr int S_STAGE = 2 * TW * 4;    // 1 KiB
 constexpr int A_COL = TT;
 constexpr int TMEM_COLS = 512;
-constexpr int NUM_DQ_WARPS = 8;
+constexpr int NUM_DQ_WARPS = 8;     // dequant warps per k-block
+constexpr int DQ_GROUPS = 2;        // groups of dequant warps taking k-blocks in turn
 constexpr int NUM_EPI_WARPS = 8;
-constexpr int THREADS = 32 * (2 + NUM_DQ_WARPS + NUM_EPI_WARPS);
+constexpr int THREADS = 32 * (2 + DQ_GROUPS * NUM_DQ_WARPS + NUM_EPI_WARPS);
 constexpr int SMEM_BYTES = STAGES * (X_STAGE + W_STAGE + S_STAGE) + 1024 + 512;
 constexpr uint32_t PEER_MASK = 0xFEFFFFFFu;  // clears the CTA-rank bit of a shared::cluster address: the even CTA
 
@@ -195,9 +196,10 @@ gemm_dequant_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                 tc_commit_pair(&bars->acc_full);
             }
         }
-    } else if (warp < 2 + NUM_DQ_WARPS) {
+    } else if (warp < 2 + DQ_GROUPS * NUM_DQ_WARPS) {
         // ---------------- dequant warps (both CTAs, own weight rows) ----------------
-        const int dq = warp - 2;
+        const int grp = (warp - 2) / NUM_DQ_WARPS;   // this group unpacks k-blocks it % DQ_GROUPS == grp
+        const int dq = (warp - 2) % NUM_DQ_WARPS;
         const int quarter = warp & 3;
         const int half = dq >> 2;
         const int row = quarter * 32 + lane;
@@ -216,6 +218,7 @@ gemm_dequant_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
         };
         for (int tile = pair; tile < tiles && ok && !*abort_flag; tile += pairs) {
             for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                if ((int)(it % DQ_GROUPS) != grp) continue;
                 const int s = it % STAGES, ai = it % ASTAGES;
                 const uint32_t ph = (it / STAGES) & 1u, aph = (it / ASTAGES) & 1u;
                 if (!mbar_wait<100>(&bars->w_full[s], ph, abort_flag, 5)) { ok = false; break; }
@@ -262,7 +265,7 @@ gemm_dequant_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
     } else {
         // ---------------- epilogue warps (both CTAs, own accumulator rows) ----------------
         const int quarter = warp & 3;
-        const int ehalf = (warp - 2 - NUM_DQ_WARPS) >> 2;
+        const int ehalf = (warp - 2 - DQ_GROUPS * NUM_DQ_WARPS) >> 2;
         const int row = quarter * 32 + lane;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         uint32_t tile_i = 0;
@@ -306,22 +309,17 @@ gemm_dequant_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
             };
             const int c0 = ehalf * (TT / 64);
             const uint32_t t0 = tmem + lane_addr + c0 * 32;
-            uint32_t va[32], vb[32];
-            tmem_ld_x32(t0, va);
 #pragma unroll 1
-            for (int i = 0; i < TT / 64; i += 2) {
+            for (int i = 0; i < TT / 64; ++i) {
+                uint32_t va[32];
+                tmem_ld_x32(t0 + i * 32, va);
                 tc_wait_ld();
-                tmem_ld_x32(t0 + (i + 1) * 32, vb);
-                emit(va, c0 + i);
-                tc_wait_ld();
-                if (i + 2 < TT / 64) {
-                    tmem_ld_x32(t0 + (i + 2) * 32, va);
-                } else {
+                if (i + 1 == TT / 64) {
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) arrive_on_even_cta(&bars->acc_empty);
                 }
-                emit(vb, c0 + i + 1);
+                emit(va, c0 + i);
             }
         }
     }
