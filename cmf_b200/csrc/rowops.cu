@@ -71,13 +71,17 @@ residual_kernel(float* __restrict__ x, const float* __restrict__ src, const floa
     constexpr int cols = 128 * NV;
     const float* sr = src + (size_t)row * cols;
     float* xr = x + (size_t)row * cols;
-    float4 d[NV];
+    // both rows (the GEMM output and the residual stream) are requested up front: the second does
+    // not depend on the statistics of the first, and twice the bytes are in flight per warp
+    float4 d[NV], xin[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) d[i] = ld4(sr + (i * 32 + lane) * 4);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) xin[i] = ld4(xr + (i * 32 + lane) * 4);
     double ss = 0.0;
 #pragma unroll
-    for (int i = 0; i < NV; ++i) {
-        d[i] = ld4(sr + (i * 32 + lane) * 4);
+    for (int i = 0; i < NV; ++i)
         ss += (double)d[i].x * d[i].x + (double)d[i].y * d[i].y + (double)d[i].z * d[i].z + (double)d[i].w * d[i].w;
-    }
     ss = warp_sum(ss);
     const double inv = 1.0 / sqrt(ss / cols + eps);
     double ss2 = 0.0;
@@ -85,7 +89,7 @@ residual_kernel(float* __restrict__ x, const float* __restrict__ src, const floa
     for (int i = 0; i < NV; ++i) {
         const int c = (i * 32 + lane) * 4;
         float4 g = ld4(w_res + c);
-        float4 xv = ld4(xr + c);
+        float4 xv = xin[i];
         float4 r;
         r.x = rms_elem(d[i].x, inv, g.x); r.y = rms_elem(d[i].y, inv, g.y);
         r.z = rms_elem(d[i].z, inv, g.z); r.w = rms_elem(d[i].w, inv, g.w);
