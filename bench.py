@@ -423,7 +423,7 @@ def main():
             # dram__bytes_read.sum + dram__bytes_write.sum of one captured launch of this kernel, the
             # gate/up GEMM of a block (N=18432, K=2304, M=8704, SwiGLU epilogue; algorithmic 224 MB; pair kernel):
             # profiles/gemm_dequant_q4t_swiglu_N18432_K2304_M8704.md
-            line["roofline"]["traffic"] = 196.5e6
+            line["roofline"]["traffic"] = 195.5e6
             line["roofline"]["traffic_launch"] = "gate/up GEMM of one block, N=18432 K=2304 M=8704"
         print(json.dumps(line), flush=True)
     dit.close()
