@@ -16,6 +16,10 @@
 //                  it by more than 8 (in log2 units), so P stays below 2^8 and the O row in TMEM
 //                  is multiplied by exp2(m_old - m_new) on the few tiles where that happens
 // While the softmax warps of tile A work, the tensor core runs tile B, and vice versa.
+// The special-function unit (16 exp2 per clock per SM) is the busiest pipe of this kernel: the
+// softmax arithmetic around it is packed (fma / add .f32x2, three-input max: one issue slot per
+// two scores) and a quarter of the exponentials are computed on the FMA pipe instead (round to
+// integer with the 1.5 * 2^23 trick, a cubic for the fraction, exponent inserted by an integer add).
 //
 // TMEM plan for head_dim <= 96 ("split" plan): S of tile A / B at columns 0 / 128, ONE P buffer
 // shared by both tiles at 256 (64 columns of packed bf16), O of tile A / B at 320 / 416.  P no
@@ -39,6 +43,7 @@ template <int HD> __host__ __device__ constexpr int p_col(int t) { return split_
 template <int HD> __host__ __device__ constexpr int r_col(int t) { return split_plan<HD>() ? 320 + t * 96 : 256 + t * 128; }
 constexpr int ATTN_TMEM_COLS = 512;
 
+
 struct AttnBars {
     uint64_t q_full;
     uint64_t k_full[KV_STAGES], k_empty[KV_STAGES];
@@ -60,7 +65,8 @@ struct AttnSmem {
     static constexpr int TOTAL = 2 * Q_TILE + KV_STAGES * (K_TILE + V_TILE) + 1024 + 256;
 };
 
-template <int HD>
+// POLY_OF_8: pairs out of every eight whose exp2 runs on the FMA pipe instead of the special-function unit
+template <int HD, int POLY_OF_8>
 __global__ void __launch_bounds__(ATTN_THREADS, 1)
 attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_vt, AttnParams p) {
@@ -266,7 +272,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #pragma unroll
                 for (int ch = 0; ch < 4; ++ch)
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) mxs[i & 7] = fmaxf(mxs[i & 7], __uint_as_float(v[ch][i]));
+                    for (int i = 0; i < 32; i += 2)
+                        mxs[(i >> 1) & 7] = max3_f32(mxs[(i >> 1) & 7], __uint_as_float(v[ch][i]), __uint_as_float(v[ch][i + 1]));
             } else {
 #pragma unroll
                 for (int ch = 0; ch < 4; ++ch)
@@ -305,15 +312,26 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     }
                 }
             }
-            float sums[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            // exp2(s * c - m) in pairs: packed FMA and packed sums (one issue slot per two elements);
+            // POLY_OF_8 of every eight pairs take the polynomial route on the FMA pipe instead of the
+            // special-function unit, which is the pipe that bounds this loop
+            uint64_t sums[4] = {0ull, 0ull, 0ull, 0ull};
             uint32_t pk[4][16];
+            const uint64_t c2 = pack_f32x2(c, c), nm2 = pack_f32x2(-m_ref, -m_ref);
 #pragma unroll
             for (int ch = 0; ch < 4; ++ch) {
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    const float e0 = ex2_approx(fmaf(__uint_as_float(v[ch][i]), c, -m_ref));
-                    const float e1 = ex2_approx(fmaf(__uint_as_float(v[ch][i + 1]), c, -m_ref));
-                    sums[(i >> 1) & 3] += e0 + e1;
+                    const uint64_t t2 = fma_f32x2(pack_f32x2(__uint_as_float(v[ch][i]), __uint_as_float(v[ch][i + 1])), c2, nm2);
+                    float t0, t1, e0, e1;
+                    unpack_f32x2(t2, t0, t1);
+                    if (((i >> 1) & 7) < POLY_OF_8) {
+                        ex2_poly_x2(t0, t1, e0, e1);
+                    } else {
+                        e0 = ex2_approx(t0);
+                        e1 = ex2_approx(t1);
+                    }
+                    sums[(i >> 1) & 3] = add_f32x2(sums[(i >> 1) & 3], pack_f32x2(e0, e1));
                     pk[ch][i >> 1] = pack_bf16(e0, e1);
                 }
                 if constexpr (!split_plan<HD>()) tmem_st_x16(tmem + lane_addr + p_col<HD>(t) + ch * 16, pk[ch]);
@@ -334,7 +352,11 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 for (int ch = 0; ch < 4; ++ch) tmem_st_x16(tmem + lane_addr + p_col<HD>(t) + ch * 16, pk[ch]);
             }
             tc_wait_st();
-            l_run += (sums[0] + sums[1]) + (sums[2] + sums[3]);
+            {
+                float s0, s1;
+                unpack_f32x2(add_f32x2(add_f32x2(sums[0], sums[1]), add_f32x2(sums[2], sums[3])), s0, s1);
+                l_run += s0 + s1;
+            }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars->p_full[t]);
@@ -385,19 +407,19 @@ int attn_smem_bytes(int hd) {
     }
 }
 
-template <int HD>
+template <int HD, int POLY>
 static int launch_hd(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_vt, const AttnParams& p,
                      cudaStream_t stream) {
     static bool configured[64] = {false};  // per instantiation and device; never repeated inside a stream capture
     int dev = 0;
     CMFC_CUDA(cudaGetDevice(&dev));
     if (!configured[dev & 63]) {
-        CMFC_CUDA(cudaFuncSetAttribute(attention_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        CMFC_CUDA(cudaFuncSetAttribute(attention_kernel<HD, POLY>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        AttnSmem<HD>::TOTAL));
         configured[dev & 63] = true;
     }
     dim3 grid((p.max_seg + 2 * QT - 1) / (2 * QT), p.nh, p.nseg);
-    attention_kernel<HD><<<grid, ATTN_THREADS, AttnSmem<HD>::TOTAL, stream>>>(tm_q, tm_k, tm_vt, p);
+    attention_kernel<HD, POLY><<<grid, ATTN_THREADS, AttnSmem<HD>::TOTAL, stream>>>(tm_q, tm_k, tm_vt, p);
     CMFC_CUDA(cudaGetLastError());
     return OK;
 }
@@ -405,10 +427,10 @@ static int launch_hd(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUt
 int launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_vt, const AttnParams& p,
                      cudaStream_t stream) {
     switch (p.hd) {
-        case 32: return launch_hd<32>(tm_q, tm_k, tm_vt, p, stream);
-        case 64: return launch_hd<64>(tm_q, tm_k, tm_vt, p, stream);
-        case 96: return launch_hd<96>(tm_q, tm_k, tm_vt, p, stream);
-        case 128: return launch_hd<128>(tm_q, tm_k, tm_vt, p, stream);
+        case 32: return launch_hd<32, 2>(tm_q, tm_k, tm_vt, p, stream);
+        case 64: return launch_hd<64, 2>(tm_q, tm_k, tm_vt, p, stream);
+        case 96: return launch_hd<96, 2>(tm_q, tm_k, tm_vt, p, stream);
+        case 128: return launch_hd<128, 2>(tm_q, tm_k, tm_vt, p, stream);
         default: return fail(ERR_UNSUPPORTED, "attention: head_dim must be 32, 64, 96 or 128");
     }
 }

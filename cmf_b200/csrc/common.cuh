@@ -290,6 +290,50 @@ __device__ __forceinline__ float ex2_approx(float x) {
     return y;
 }
 
+// ---- packed f32x2 arithmetic: one issue slot for two lanes of the FMA pipe ----
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ float max3_f32(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+// 2^t for a pair without the special-function unit: n = round(t) through the 1.5 * 2^23 trick,
+// a cubic for 2^(t - n) on [-0.5, 0.5] (relative error 7.5e-5, far below the bf16 rounding the
+// result gets), n added into the exponent field.  t is clamped at -126.
+__device__ __forceinline__ void ex2_poly_x2(float t0, float t1, float& e0, float& e1) {
+    const float MAGIC = 12582912.0f;
+    const uint64_t t = pack_f32x2(fmaxf(t0, -126.0f), fmaxf(t1, -126.0f));
+    const uint64_t r = add_f32x2(t, pack_f32x2(MAGIC, MAGIC));
+    const uint64_t n = add_f32x2(r, pack_f32x2(-MAGIC, -MAGIC));
+    const uint64_t f = fma_f32x2(n, pack_f32x2(-1.0f, -1.0f), t);
+    uint64_t q = fma_f32x2(f, pack_f32x2(0.0551716648042202f, 0.0551716648042202f),
+                           pack_f32x2(0.2426111251115799f, 0.2426111251115799f));
+    q = fma_f32x2(q, f, pack_f32x2(0.6932609677314758f, 0.6932609677314758f));
+    q = fma_f32x2(q, f, pack_f32x2(0.9999280571937561f, 0.9999280571937561f));
+    float r0, r1, q0, q1;
+    unpack_f32x2(r, r0, r1);
+    unpack_f32x2(q, q0, q1);
+    e0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(r0) << 23));
+    e1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(r1) << 23));
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
