@@ -176,68 +176,97 @@ layernorm_scale_kernel(const float* __restrict__ x, const float* __restrict__ sc
         default: break;                                                          \
     }
 
-// qk-norm + RoPE: a half-warp owns one (token, head); each lane holds hd/32 interleaved pairs.
-template <int PPL>  // pairs per lane = hd / 32
-__global__ void __launch_bounds__(256)
+// qk-norm + RoPE: four lanes own one (token, head); of every 32 consecutive elements of the head a
+// lane holds eight (four rotation pairs): two 16-byte loads, one 16-byte store, and the f64
+// square root and division of the statistic are paid once per eight heads of a warp.
+template <int PPL>  // hd / 32
+__global__ void __launch_bounds__(256, PPL <= 3 ? 4 : 2)
 qk_rope_kernel(const float* __restrict__ qkv, int n, int nh, int nkv, const float* __restrict__ norm_q,
                const float* __restrict__ norm_k, const double* __restrict__ cos_t, const double* __restrict__ sin_t,
                __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_out) {
     constexpr int hd = 32 * PPL;
     const int heads = nh + nkv;
-    const long item = (long)blockIdx.x * 16 + (threadIdx.x >> 4);
-    const int l = threadIdx.x & 15;
+    const long item = (long)blockIdx.x * 64 + (threadIdx.x >> 2);
+    const int l = threadIdx.x & 3;
     const bool active = item < (long)n * heads;
     const int tok = active ? (int)(item / heads) : 0;
     const int h = active ? (int)(item % heads) : 0;
     const bool is_q = h < nh;
     const int ld_in = (nh + 2 * nkv) * hd;
-    const float* src = qkv + (size_t)tok * ld_in + (size_t)h * hd;  // q heads then k heads are contiguous
-    const float* w = is_q ? norm_q : norm_k;
-    float2 v[PPL];
+    const float* src = qkv + (size_t)tok * ld_in + (size_t)h * hd + l * 8;  // q heads then k heads are contiguous
+    const float* w = (is_q ? norm_q : norm_k) + l * 8;
+    float4 v[PPL][2];
+#pragma unroll
+    for (int g = 0; g < PPL; ++g) {
+        v[g][0] = ld4(src + g * 32);
+        v[g][1] = ld4(src + g * 32 + 4);
+    }
     double ss = 0.0;
 #pragma unroll
-    for (int i = 0; i < PPL; ++i) {
-        v[i] = *reinterpret_cast<const float2*>(src + 2 * (i * 16 + l));
-        ss += (double)v[i].x * v[i].x + (double)v[i].y * v[i].y;
-    }
+    for (int g = 0; g < PPL; ++g)
 #pragma unroll
-    for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        for (int u = 0; u < 2; ++u)
+            ss += (double)v[g][u].x * v[g][u].x + (double)v[g][u].y * v[g][u].y + (double)v[g][u].z * v[g][u].z +
+                  (double)v[g][u].w * v[g][u].w;
+    ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+    ss += __shfl_xor_sync(0xffffffffu, ss, 1);
     const double inv = 1.0 / sqrt(ss / hd + 1e-5);
     if (!active) return;
-    __nv_bfloat16* dst = is_q ? q_out + (size_t)tok * nh * hd + (size_t)h * hd
-                              : k_out + (size_t)tok * nkv * hd + (size_t)(h - nh) * hd;
+    __nv_bfloat16* dst = (is_q ? q_out + (size_t)tok * nh * hd + (size_t)h * hd
+                               : k_out + (size_t)tok * nkv * hd + (size_t)(h - nh) * hd) + l * 8;
+    const double* ct = cos_t + (size_t)tok * (hd / 2) + l * 4;
+    const double* st = sin_t + (size_t)tok * (hd / 2) + l * 4;
 #pragma unroll
-    for (int i = 0; i < PPL; ++i) {
-        const int j = i * 16 + l;
-        const float2 g = *reinterpret_cast<const float2*>(w + 2 * j);
-        const double a = (double)rms_elem(v[i].x, inv, g.x), b = (double)rms_elem(v[i].y, inv, g.y);
-        const double c = cos_t[(size_t)tok * (hd / 2) + j], s = sin_t[(size_t)tok * (hd / 2) + j];
-        const float re = (float)(a * c - b * s), im = (float)(a * s + b * c);
-        *reinterpret_cast<uint32_t*>(dst + 2 * j) = pack_bf16(re, im);
+    for (int g = 0; g < PPL; ++g) {
+        const float4 g0 = ld4(w + g * 32), g1 = ld4(w + g * 32 + 4);
+        const double2 c01 = *reinterpret_cast<const double2*>(ct + g * 16), c23 = *reinterpret_cast<const double2*>(ct + g * 16 + 2);
+        const double2 s01 = *reinterpret_cast<const double2*>(st + g * 16), s23 = *reinterpret_cast<const double2*>(st + g * 16 + 2);
+        auto rot = [&](float x, float y, float gx, float gy, double c, double s) {
+            const double a = (double)rms_elem(x, inv, gx), b = (double)rms_elem(y, inv, gy);
+            return pack_bf16((float)(a * c - b * s), (float)(a * s + b * c));
+        };
+        uint4 o;
+        o.x = rot(v[g][0].x, v[g][0].y, g0.x, g0.y, c01.x, s01.x);
+        o.y = rot(v[g][0].z, v[g][0].w, g0.z, g0.w, c01.y, s01.y);
+        o.z = rot(v[g][1].x, v[g][1].y, g1.x, g1.y, c23.x, s23.x);
+        o.w = rot(v[g][1].z, v[g][1].w, g1.z, g1.w, c23.y, s23.y);
+        *reinterpret_cast<uint4*>(dst + g * 32) = o;
     }
 }
 
-// V [n, ld_in] f32 (columns v_off + [0, width)) -> V^T bf16 [width, vt_pitch], 32x32 tiles via
-// shared memory.  Segment z's tokens land at columns seg_table[nseg+1+z] + local index, so each
-// segment starts on an 8-column boundary; pad columns are written as zero.
+// V [n, ld_in] f32 (columns v_off + [0, width)) -> V^T bf16 [width, vt_pitch], tiles of 64 tokens x
+// 64 dims via shared memory (256-byte reads, 128-byte writes).  Segment z's tokens land at columns
+// seg_table[nseg+1+z] + local index, so each segment starts on an 8-column boundary; pad columns
+// are written as zero.
 __global__ void __launch_bounds__(256)
 v_transpose_kernel(const float* __restrict__ qkv, int ld_in, int v_off, int width, __nv_bfloat16* __restrict__ vt,
                    int vt_pitch, const int* __restrict__ seg_table, int nseg) {
-    __shared__ float tile[32][33];
+    __shared__ float tile[64][65];
     const int z = blockIdx.z;
     const int seg0 = seg_table[z], len = seg_table[z + 1] - seg0, col0 = seg_table[nseg + 1 + z];
-    const int t0 = blockIdx.x * 32, d0 = blockIdx.y * 32;
+    const int t0 = blockIdx.x * 64, d0 = blockIdx.y * 64;
     if (t0 >= len) return;
     const int padded = (len + 7) & ~7;
-    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-    for (int r = ty; r < 32; r += 8) {
-        const int tok = t0 + r;
-        tile[r][tx] = (tok < len && d0 + tx < width) ? qkv[(size_t)(seg0 + tok) * ld_in + v_off + d0 + tx] : 0.0f;
+    const int lane = threadIdx.x & 31, wp = threadIdx.x >> 5;
+    float a[8], b[8];  // sixteen loads in flight per thread
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int tok = t0 + wp + 8 * i;
+        const float* src = qkv + (size_t)(seg0 + tok) * ld_in + v_off + d0;
+        a[i] = (tok < len && d0 + lane < width) ? src[lane] : 0.0f;
+        b[i] = (tok < len && d0 + lane + 32 < width) ? src[lane + 32] : 0.0f;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        tile[wp + 8 * i][lane] = a[i];
+        tile[wp + 8 * i][lane + 32] = b[i];
     }
     __syncthreads();
-    for (int r = ty; r < 32; r += 8) {
-        const int d = d0 + r, tok = t0 + tx;
-        if (d < width && tok < padded) vt[(size_t)d * vt_pitch + col0 + tok] = __float2bfloat16_rn(tile[tx][r]);
+#pragma unroll
+    for (int r = wp; r < 64; r += 8) {
+        const int d = d0 + r, tok = t0 + 2 * lane;  // padded is even: a token pair is inside or outside together
+        if (d < width && tok < padded)
+            *reinterpret_cast<uint32_t*>(vt + (size_t)d * vt_pitch + col0 + tok) = pack_bf16(tile[2 * lane][r], tile[2 * lane + 1][r]);
     }
 }
 
@@ -498,7 +527,7 @@ void launch_qk_rope_pack(const float* qkv, int n, int nh, int nkv, int hd, const
                          __nv_bfloat16* k, __nv_bfloat16* vt, int vt_pitch, const int* seg_table, int nseg, int max_seg,
                          cudaStream_t s) {
     const long items = (long)n * (nh + nkv);
-    const int grid = (int)((items + 15) / 16);
+    const int grid = (int)((items + 63) / 64);
     switch (hd / 32) {
         case 1: qk_rope_kernel<1><<<grid, 256, 0, s>>>(qkv, n, nh, nkv, norm_q, norm_k, cos_t, sin_t, q, k); break;
         case 2: qk_rope_kernel<2><<<grid, 256, 0, s>>>(qkv, n, nh, nkv, norm_q, norm_k, cos_t, sin_t, q, k); break;
@@ -507,7 +536,7 @@ void launch_qk_rope_pack(const float* qkv, int n, int nh, int nkv, int hd, const
         default: break;
     }
     const int ld_in = (nh + 2 * nkv) * hd, width = nkv * hd;
-    dim3 g((max_seg + 31) / 32, (width + 31) / 32, nseg);
+    dim3 g((max_seg + 63) / 64, (width + 63) / 64, nseg);
     v_transpose_kernel<<<g, 256, 0, s>>>(qkv, ld_in, (nh + nkv) * hd, width, vt, vt_pitch, seg_table, nseg);
 }
 void launch_interleave_f32(float* dst, int dst_stride, int dst_off, const float* src, size_t count, cudaStream_t s) {
