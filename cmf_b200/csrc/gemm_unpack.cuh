@@ -19,30 +19,41 @@ __device__ __forceinline__ void unpack_q8_word(uint32_t w, uint32_t& o0, uint32_
     asm("sub.bf16x2 %0, %1, %2;" : "=r"(o1) : "r"(v1), "r"(c1));
 }
 
-// nibble at bit position p of ``w`` -> exact f32 (nib-8)*s: the nibble is OR-ed into the
-// mantissa of 2^23, the bias (2^23 + 8*2^p) is subtracted exactly, and the result is scaled
-// by s*2^-p (a power-of-two rescale, so the single rounding equals that of (nib-8)*s).
-template <int P>
-__device__ __forceinline__ float nib_times(uint32_t w, float s_shifted) {
-    float f = __uint_as_float((w & (0xFu << P)) | 0x4B000000u);
-    f = __fsub_rn(f, 8388608.0f + 8.0f * (float)(1u << P));
-    return __fmul_rn(f, s_shifted);
+// Nibbles at bit positions PA of ``wa`` and PB of ``wb`` -> the bf16 pair of the exact f32 products
+// (nib-8)*s: each nibble is OR-ed into the mantissa of 2^23, the bias (2^23 + 8*2^P) is subtracted
+// exactly, and the result is scaled by s*2^-P (a power-of-two rescale, so the single rounding
+// equals that of (nib-8)*s).  Subtract and multiply are packed f32x2 operations (IEEE round to
+// nearest per lane, one issue slot for the pair).
+template <int PA, int PB>
+__device__ __forceinline__ uint32_t nib_pair_times(uint32_t wa, uint32_t wb, uint64_t s_shifted) {
+    const uint64_t f = pack_f32x2(__uint_as_float((wa & (0xFu << PA)) | 0x4B000000u),
+                                  __uint_as_float((wb & (0xFu << PB)) | 0x4B000000u));
+    const uint64_t d = add_f32x2(f, pack_f32x2(-(8388608.0f + 8.0f * (float)(1u << PA)),
+                                               -(8388608.0f + 8.0f * (float)(1u << PB))));
+    float lo, hi;
+    unpack_f32x2(mul_f32x2(d, s_shifted), lo, hi);
+    return pack_bf16(lo, hi);
 }
 
 struct Q4Scales {
-    float s0, s4, s8, s12, s16;
-    __device__ __forceinline__ explicit Q4Scales(float s)
-        : s0(s), s4(s * 0.0625f), s8(s * 0.00390625f), s12(s * 0.000244140625f), s16(s * 1.52587890625e-05f) {}
+    uint64_t s0_4, s4_8, s8_12, s12_16;  // (s * 2^-a, s * 2^-b) pairs
+    __device__ __forceinline__ explicit Q4Scales(float s) {
+        const float s4 = s * 0.0625f, s8 = s * 0.00390625f, s12 = s * 0.000244140625f, s16 = s * 1.52587890625e-05f;
+        s0_4 = pack_f32x2(s, s4);
+        s4_8 = pack_f32x2(s4, s8);
+        s8_12 = pack_f32x2(s8, s12);
+        s12_16 = pack_f32x2(s12, s16);
+    }
 };
 
 // One plane word (elements 0..7 at nibble positions 0,4,1,5,2,6,3,7) -> four bf16x2 registers.
 // f32 route, any f32 scale (q4tp ladder scales): exact product, one rounding to bf16.
 __device__ __forceinline__ void unpack_q4_word(uint32_t w, const Q4Scales& sc, uint32_t* o) {
-    uint32_t hi = w >> 12;  // positions 4..7 -> bits 4, 8, 12, 16
-    o[0] = pack_bf16(nib_times<0>(w, sc.s0), nib_times<4>(hi, sc.s4));
-    o[1] = pack_bf16(nib_times<4>(w, sc.s4), nib_times<8>(hi, sc.s8));
-    o[2] = pack_bf16(nib_times<8>(w, sc.s8), nib_times<12>(hi, sc.s12));
-    o[3] = pack_bf16(nib_times<12>(w, sc.s12), nib_times<16>(hi, sc.s16));
+    const uint32_t hi = w >> 12;  // positions 4..7 -> bits 4, 8, 12, 16
+    o[0] = nib_pair_times<0, 4>(w, hi, sc.s0_4);
+    o[1] = nib_pair_times<4, 8>(w, hi, sc.s4_8);
+    o[2] = nib_pair_times<8, 12>(w, hi, sc.s8_12);
+    o[3] = nib_pair_times<12, 16>(w, hi, sc.s12_16);
 }
 
 // bf16x2 route for q4_tiled, whose scale is an f16 value s = hi + lo with hi (8 significant bits)
