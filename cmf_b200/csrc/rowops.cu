@@ -10,7 +10,7 @@
 namespace cmfc {
 namespace {
 
-constexpr int ROW_WARPS = 8;  // warps (rows) per block for the row kernels
+constexpr int ROW_WARPS = 2;  // warps (rows) per block for the row kernels: small blocks keep the tail of a launch short
 
 __device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
 __device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
@@ -179,14 +179,15 @@ layernorm_scale_kernel(const float* __restrict__ x, const float* __restrict__ sc
 // qk-norm + RoPE: four lanes own one (token, head); of every 32 consecutive elements of the head a
 // lane holds eight (four rotation pairs): two 16-byte loads, one 16-byte store, and the f64
 // square root and division of the statistic are paid once per eight heads of a warp.
+constexpr int ROPE_THREADS = 128;
 template <int PPL>  // hd / 32
-__global__ void __launch_bounds__(256, PPL <= 3 ? 4 : 2)
+__global__ void __launch_bounds__(ROPE_THREADS, PPL <= 3 ? 8 : 4)
 qk_rope_kernel(const float* __restrict__ qkv, int n, int nh, int nkv, const float* __restrict__ norm_q,
                const float* __restrict__ norm_k, const double* __restrict__ cos_t, const double* __restrict__ sin_t,
                __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_out) {
     constexpr int hd = 32 * PPL;
     const int heads = nh + nkv;
-    const long item = (long)blockIdx.x * 64 + (threadIdx.x >> 2);
+    const long item = (long)blockIdx.x * (ROPE_THREADS / 4) + (threadIdx.x >> 2);
     const int l = threadIdx.x & 3;
     const bool active = item < (long)n * heads;
     const int tok = active ? (int)(item / heads) : 0;
@@ -527,12 +528,12 @@ void launch_qk_rope_pack(const float* qkv, int n, int nh, int nkv, int hd, const
                          __nv_bfloat16* k, __nv_bfloat16* vt, int vt_pitch, const int* seg_table, int nseg, int max_seg,
                          cudaStream_t s) {
     const long items = (long)n * (nh + nkv);
-    const int grid = (int)((items + 63) / 64);
+    const int grid = (int)((items + ROPE_THREADS / 4 - 1) / (ROPE_THREADS / 4));
     switch (hd / 32) {
-        case 1: qk_rope_kernel<1><<<grid, 256, 0, s>>>(qkv, n, nh, nkv, norm_q, norm_k, cos_t, sin_t, q, k); break;
-        case 2: qk_rope_kernel<2><<<grid, 256, 0, s>>>(qkv, n, nh, nkv, norm_q, norm_k, cos_t, sin_t, q, k); break;
-        case 3: qk_rope_kernel<3><<<grid, 256, 0, s>>>(qkv, n, nh, nkv, norm_q, norm_k, cos_t, sin_t, q, k); break;
-        case 4: qk_rope_kernel<4><<<grid, 256, 0, s>>>(qkv, n, nh, nkv, norm_q, norm_k, cos_t, sin_t, q, k); break;
+        case 1: qk_rope_kernel<1><<<grid, ROPE_THREADS, 0, s>>>(qkv, n, nh, nkv, norm_q, norm_k, cos_t, sin_t, q, k); break;
+        case 2: qk_rope_kernel<2><<<grid, ROPE_THREADS, 0, s>>>(qkv, n, nh, nkv, norm_q, norm_k, cos_t, sin_t, q, k); break;
+        case 3: qk_rope_kernel<3><<<grid, ROPE_THREADS, 0, s>>>(qkv, n, nh, nkv, norm_q, norm_k, cos_t, sin_t, q, k); break;
+        case 4: qk_rope_kernel<4><<<grid, ROPE_THREADS, 0, s>>>(qkv, n, nh, nkv, norm_q, norm_k, cos_t, sin_t, q, k); break;
         default: break;
     }
     const int ld_in = (nh + 2 * nkv) * hd, width = nkv * hd;
