@@ -14,6 +14,7 @@
 // Every wait is bounded; the pair leaves through a cluster barrier so that neither CTA exits
 // while the other may still touch its shared or tensor memory.
 #include <cooperative_groups.h>
+#include <algorithm>
 
 #include "common.cuh"
 #include "gemm_unpack.cuh"
@@ -96,10 +97,37 @@ __device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
         : "memory");
 }
 
+// Work of one CTA pair: whole tiles pair, pair + pairs, ... and, when the launch cuts the tiles of its
+// last partial wave along K (splits > 1), at most a few K slices of those tiles.
+struct Unit {
+    int tile, kb0, kb1;
+    int slot;  // < 0: whole tile, the epilogue writes the output; else the partial-sum slot
+};
+__device__ __forceinline__ bool unit_at(int i, int pair, int pairs, int tiles, int kblocks, int splits, Unit& u) {
+    const int waves = splits > 1 ? tiles / pairs : (tiles + pairs - 1) / pairs;
+    if (i < waves) {
+        u.tile = pair + i * pairs;
+        u.kb0 = 0;
+        u.kb1 = kblocks;
+        u.slot = -1;
+        return u.tile < tiles;
+    }
+    if (splits <= 1) return false;
+    const int rem = tiles - waves * pairs;
+    const int q = pair + (i - waves) * pairs;
+    if (q >= rem * splits) return false;
+    const int sl = q % splits;
+    u.tile = waves * pairs + q / splits;
+    u.kb0 = (int)((long)sl * kblocks / splits);
+    u.kb1 = (int)((long)(sl + 1) * kblocks / splits);
+    u.slot = q;
+    return true;
+}
+
 template <int WKIND>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_dequant_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
-                         const __grid_constant__ CUtensorMap tm_s, GemmParams p) {
+                         const __grid_constant__ CUtensorMap tm_s, GemmParams p, int splits) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* x_smem = smem;
@@ -152,9 +180,11 @@ gemm_dequant_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
         // ---------------- TMA producer (both CTAs) ----------------
         if (elect_one()) {
             uint32_t it = 0;
-            for (int tile = pair; tile < tiles && !*abort_flag; tile += pairs) {
+            Unit u;
+            for (int ui = 0; unit_at(ui, pair, pairs, tiles, kblocks, splits, u) && !*abort_flag; ++ui) {
+                const int tile = u.tile;
                 const int n0 = (tile % tiles_n) * (2 * TW) + rank * TW, m0 = (tile / tiles_n) * TT + rank * TH;
-                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                for (int kb = u.kb0; kb < u.kb1; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1u;
                     if (!mbar_wait<200>(&bars->empty[s], ph ^ 1u, abort_flag, 1)) break;
@@ -176,11 +206,12 @@ gemm_dequant_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
         if (rank == 0 && elect_one()) {
             constexpr uint32_t IDESC = idesc_bf16_f32(2 * TW, TT);
             uint32_t it = 0, tile_i = 0;
-            for (int tile = pair; tile < tiles && !*abort_flag; tile += pairs, ++tile_i) {
+            Unit u;
+            for (int ui = 0; unit_at(ui, pair, pairs, tiles, kblocks, splits, u) && !*abort_flag; ++ui, ++tile_i) {
                 if (!mbar_wait(&bars->acc_empty, (tile_i & 1u) ^ 1u, abort_flag, 2)) break;
                 tc_fence_after();
                 bool ok = true;
-                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                for (int kb = u.kb0; kb < u.kb1; ++kb, ++it) {
                     const int s = it % STAGES, ai = it % ASTAGES;
                     const uint32_t ph = (it / STAGES) & 1u, aph = (it / ASTAGES) & 1u;
                     if (!mbar_wait(&bars->x_full[s], ph, abort_flag, 3) ||
@@ -189,7 +220,7 @@ gemm_dequant_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                     const uint32_t xs = smem_u32(x_smem + s * X_STAGE);
 #pragma unroll
                     for (int j = 0; j < BK / 16; ++j)
-                        mma_ts_pair(tmem, tmem + A_COL + ai * 32 + j * 8, smem_desc_kmajor(xs + j * 32, 128), IDESC, (kb | j) != 0);
+                        mma_ts_pair(tmem, tmem + A_COL + ai * 32 + j * 8, smem_desc_kmajor(xs + j * 32, 128), IDESC, kb != u.kb0 || j != 0);
                     tc_commit_pair(&bars->a_empty[ai]);
                 }
                 if (!ok) break;
@@ -216,8 +247,9 @@ gemm_dequant_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                 pending = -1;
             }
         };
-        for (int tile = pair; tile < tiles && ok && !*abort_flag; tile += pairs) {
-            for (int kb = 0; kb < kblocks; ++kb, ++it) {
+        Unit u;
+        for (int ui = 0; unit_at(ui, pair, pairs, tiles, kblocks, splits, u) && ok && !*abort_flag; ++ui) {
+            for (int kb = u.kb0; kb < u.kb1; ++kb, ++it) {
                 if ((int)(it % DQ_GROUPS) != grp) continue;
                 const int s = it % STAGES, ai = it % ASTAGES;
                 const uint32_t ph = (it / STAGES) & 1u, aph = (it / ASTAGES) & 1u;
@@ -269,7 +301,9 @@ gemm_dequant_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
         const int row = quarter * 32 + lane;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         uint32_t tile_i = 0;
-        for (int tile = pair; tile < tiles && !*abort_flag; tile += pairs, ++tile_i) {
+        Unit u;
+        for (int ui = 0; unit_at(ui, pair, pairs, tiles, kblocks, splits, u) && !*abort_flag; ++ui, ++tile_i) {
+            const int tile = u.tile;
             const int n0 = (tile % tiles_n) * (2 * TW) + rank * TW, m0 = (tile / tiles_n) * TT;
             if (!mbar_wait<80>(&bars->acc_full, tile_i & 1u, abort_flag, 6)) break;
             tc_fence_after();
@@ -279,7 +313,13 @@ gemm_dequant_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
             auto emit = [&](const uint32_t (&v)[32], int c) {
                 const int mb = m0 + c * 32;
                 if (mb >= p.M) return;
-                if (p.mode == GEMM_OUT_F32) {
+                if (u.slot >= 0) {
+                    // K slice of a tile: partial sums, [token in tile][row in tile]
+                    float* out = p.splitk_ws + ((size_t)u.slot * TT + c * 32) * (2 * TW) + rank * TW + row;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (mb + j < p.M) out[(size_t)j * (2 * TW)] = __uint_as_float(v[j]) * rs;
+                } else if (p.mode == GEMM_OUT_F32) {
                     float* out = reinterpret_cast<float*>(p.out) + (size_t)mb * p.ldo + n;
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
@@ -335,6 +375,27 @@ gemm_dequant_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
     if (threadIdx.x == 0 && bars->abort_flag) atomicCAS(p.status, 0u, 0x400u | bars->abort_flag);
 }
 
+// Adds the K slices of every split tile in slice order and writes the f32 output.
+// grid (split tiles, 16): a block covers 16 of the tile's 256 tokens.
+__global__ void __launch_bounds__(256)
+gemm_splitk_reduce_kernel(const float* __restrict__ ws, int splits, int first_tile, int tiles_n, int M, float* __restrict__ out,
+                          int ldo) {
+    const int r = blockIdx.x, tile = first_tile + r;
+    const int n0 = (tile % tiles_n) * (2 * TW), m0 = (tile / tiles_n) * TT;
+    const int col = (threadIdx.x & 63) * 4;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int mi = blockIdx.y * 16 + i * 4 + (threadIdx.x >> 6);
+        if (m0 + mi >= M) continue;
+        float4 acc = *reinterpret_cast<const float4*>(ws + (((size_t)r * splits) * TT + mi) * (2 * TW) + col);
+        for (int sl = 1; sl < splits; ++sl) {
+            const float4 v = *reinterpret_cast<const float4*>(ws + (((size_t)r * splits + sl) * TT + mi) * (2 * TW) + col);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        *reinterpret_cast<float4*>(out + (size_t)(m0 + mi) * ldo + n0 + col) = acc;
+    }
+}
+
 }  // namespace
 
 bool gemm_pair_supported(const GemmParams& p) { return p.K % BK == 0 && p.N % (2 * TW) == 0 && p.M > 0; }
@@ -366,7 +427,21 @@ int launch_gemm_dequant_pair(int wkind, const CUtensorMap& tm_x, const CUtensorM
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    CMFC_CUDA(cudaLaunchKernelEx(&cfg, kern, tm_x, tm_w, tm_s, p));
+    // A last wave that fills less than half of the pairs is cut along K instead: its tiles become
+    // `splits` slices each, spread over all pairs (one slice per pair at most).
+    int splits = 1;
+    const int kblocks = p.K / BK, rem = tiles % pairs;
+    if (p.mode == GEMM_OUT_F32 && p.splitk_ws && tiles > pairs && rem > 0 && 2 * rem <= pairs && p.ldo % 4 == 0 &&
+        (reinterpret_cast<uintptr_t>(p.out) & 15) == 0) {
+        splits = std::min(pairs / rem, kblocks / 4);
+        if (splits < 2) splits = 1;
+    }
+    CMFC_CUDA(cudaLaunchKernelEx(&cfg, kern, tm_x, tm_w, tm_s, p, splits));
+    if (splits > 1) {
+        gemm_splitk_reduce_kernel<<<dim3(rem, TT / 16), 256, 0, stream>>>(p.splitk_ws, splits, tiles - rem, p.N / (2 * TW), p.M,
+                                                                        reinterpret_cast<float*>(p.out), p.ldo);
+        CMFC_CUDA(cudaGetLastError());
+    }
     return OK;
 }
 

@@ -19,7 +19,12 @@ struct GemmParams {
     int mode;
     const float* row_scale;  // q8 only: [N]
     uint32_t* status;        // device word; a kernel that ran out of wait budget records the site
+    // pair kernel, f32 output only: the tiles of a last, mostly empty wave are cut along K into
+    // slices that spread over all CTA pairs; the slices' partial sums land here ([slot][256 tokens][256
+    // rows] f32, at most one slot per CTA pair) and a second kernel adds them in slice order
+    float* splitk_ws = nullptr;
 };
+constexpr size_t GEMM_SPLITK_SLOT_BYTES = 256 * 256 * 4;
 
 int gemm_smem_bytes();
 int gemm_tile_tokens();  // rows of the activation TMA box

@@ -158,6 +158,7 @@ int ctx_set_device(int device) {
             l2[h] = log2f(f);
             e2[h] = exp2f(f);
         }
+        CMFC_CUDA(cudaMalloc(&c->splitk_ws, (size_t)(c->num_sms / 2) * GEMM_SPLITK_SLOT_BYTES));
         CMFC_CUDA(cudaMalloc(&c->log2_lut, 65536 * 4));
         CMFC_CUDA(cudaMalloc(&c->exp2_lut, 65536 * 4));
         CMFC_CUDA(cudaMemcpy(c->log2_lut, l2.data(), 65536 * 4, cudaMemcpyHostToDevice));
@@ -578,6 +579,8 @@ int dev_gemm(Context* c, DevWeight* w, const __nv_bfloat16* x, int M, void* out,
     p.out = out; p.ldo = ldo; p.mode = mode;
     p.row_scale = w->dtype == DT_Q8 ? w->scales : nullptr;
     p.status = c->status;
+    const char* split_env = getenv("CMFC_GEMM_SPLITK");  // "0": never cut a last partial wave along K
+    p.splitk_ws = (split_env && split_env[0] == '0') ? nullptr : c->splitk_ws;
     const int wkind = w->dtype == DT_Q8 ? 0 : (w->dtype == DT_Q4TP ? 1 : 2);
     // CTA-pair kernel (2-SM MMA) whenever the weight rows tile by 256 and there is at least one
     // tile per pair of SMs; otherwise the single-CTA kernel.  CMFC_GEMM_PAIR=0 forces the latter.

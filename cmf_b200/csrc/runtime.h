@@ -91,6 +91,7 @@ struct Context {
     std::vector<std::pair<SegTable, DevBuf>> seg_cache;  // a few recent segmentations, each with its device table
     DevBuf resident_x;                 // hidden state kept between chained dit_block_seg calls
     size_t resident_len = 0;
+    float* splitk_ws = nullptr;        // partial sums of the pair GEMM's K slices: one slot per CTA pair
     float* log2_lut = nullptr;         // [65536] log2f of every f16 value (host libm)
     float* exp2_lut = nullptr;         // [65536] exp2f of every f16 value
     uint64_t launches = 0;

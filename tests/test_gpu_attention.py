@@ -41,3 +41,24 @@ def test_attention_sharp_and_flat_rows():
     want = attention_seq(q.reshape(n, -1), k.reshape(n, -1), v.reshape(n, -1), nh, nkv, hd)
     assert rel_l2(out, want) < 6e-3
     assert rel_l2(out.reshape(n, nh, hd)[:, 1], np.broadcast_to(v[:, 1].mean(0), (n, hd))) < 6e-3
+
+
+def test_attention_rising_scores_wide_range():
+    """Scores that rise by ~30 log2 units per key tile: the running maximum moves on every tile (O is
+    rescaled each time) and the early keys end up more than 2^-126 below the final maximum, which is
+    where the exponentials computed without the special-function unit clamp their argument."""
+    from cmf_b200 import gpu
+    nh, nkv, hd, n = 6, 2, 96, 700
+    rng = np.random.default_rng(11)
+    q = rng.standard_normal((n, nh, hd)).astype(np.float32)
+    k = rng.standard_normal((n, nkv, hd)).astype(np.float32)
+    q[:, :, 0] = 4.0
+    k[:, :, 0] = 300.0 * np.arange(n, dtype=np.float32)[:, None] / n
+    q, k = oc.bf16_round(q), oc.bf16_round(k)
+    v = oc.bf16_round(rng.standard_normal((n, nkv, hd)).astype(np.float32))
+    out = np.empty((n, nh * hd), np.float32)
+    scale = 1.0 / np.sqrt(hd)
+    gpu.dit_attention(q.transpose(1, 0, 2), k.transpose(1, 0, 2), v.transpose(1, 0, 2), nh, nkv, n, hd, scale, out)
+    want = attention_seq(q.reshape(n, -1), k.reshape(n, -1), v.reshape(n, -1), nh, nkv, hd)
+    assert np.isfinite(out).all()
+    assert rel_l2(out, want) < 6e-3, rel_l2(out, want)

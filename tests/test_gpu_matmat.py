@@ -138,7 +138,8 @@ def test_qkv_and_ffn(tmp_path, codecs):
 @pytest.mark.parametrize("M", [4352, 2700])
 def test_pair_kernel_equals_single_cta_kernel(tmp_path, monkeypatch, dt, M):
     """The CTA-pair GEMM (2-SM MMA, 256 x 256 tiles) and the single-CTA GEMM (128 x 256 tiles) feed
-    the tensor core the same operands in the same k order: same bits out.  M = 2700 leaves a ragged
+    the tensor core the same operands in the same k order: same bits out (with the K split of the
+    last partial wave off, which adds partial sums in another order).  M = 2700 leaves a ragged
     last token tile whose second half is entirely out of range."""
     from cmf_b200 import Model, gpu
     rng = np.random.default_rng(3)
@@ -149,8 +150,49 @@ def test_pair_kernel_equals_single_cta_kernel(tmp_path, monkeypatch, dt, M):
     single_weight_file(path, [("w", dt, w)])
     with Model(path) as m:
         monkeypatch.setenv("CMFC_GEMM_PAIR", "1")
+        monkeypatch.setenv("CMFC_GEMM_SPLITK", "0")
         a = _call(gpu, dt, m, m.index("w"), x, N, K)
         monkeypatch.setenv("CMFC_GEMM_PAIR", "0")
         b = _call(gpu, dt, m, m.index("w"), x, N, K)
     assert np.isfinite(a).all()
     assert np.array_equal(a, b)
+
+
+@pytest.mark.parametrize("dt", [oc.Q8_ROW, oc.Q4_TILED, oc.Q4TP])
+@pytest.mark.parametrize("M,K,N", [(4352, 2304, 9216), (2700, 2304, 9216), (8704, 9216, 2304), (8704, 2304, 2304)])
+def test_pair_kernel_k_split_of_last_wave(tmp_path, monkeypatch, dt, M, K, N):
+    """These shapes leave a last wave of tiles that fills less than half of the 74 CTA pairs (20, 26,
+    10 and 10 tiles); the kernel cuts those tiles along K into slices for all pairs and a second
+    kernel adds the slices in order.  Same result as the unsplit kernel up to the f32 summation
+    order, identical from run to run, and every tile outside the last wave bit-identical."""
+    from cmf_b200 import Model, gpu
+    rng = np.random.default_rng(5)
+    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    x = oc.bf16_round(rng.standard_normal((M, K)).astype(np.float32))
+    path = str(tmp_path / "w.cmf")
+    single_weight_file(path, [("w", dt, w)])
+    with Model(path) as m:
+        monkeypatch.setenv("CMFC_GEMM_PAIR", "1")
+        monkeypatch.setenv("CMFC_GEMM_SPLITK", "1")
+        a = _call(gpu, dt, m, m.index("w"), x, N, K)
+        a2 = _call(gpu, dt, m, m.index("w"), x, N, K)
+        monkeypatch.setenv("CMFC_GEMM_SPLITK", "0")
+        b = _call(gpu, dt, m, m.index("w"), x, N, K)
+    assert np.isfinite(a).all()
+    assert np.array_equal(a, a2)
+    # the tensor core accumulates a tile's K = 2304 ... 9216 products in f32 inside the MMA; adding seven
+    # shorter partial sums afterwards changes the split tiles by a few 1e-6 relative (measured 1.4e-6
+    # over the whole output for K = 9216, where 10 of 306 tiles are split)
+    assert rel_l2(a, b) < 5e-6, rel_l2(a, b)
+    tiles_n, tiles_m = N // 256, (M + 255) // 256
+    full = (tiles_n * tiles_m) // 74 * 74
+    assert full < tiles_n * tiles_m
+    differs = 0
+    for tile in range(tiles_n * tiles_m):
+        n0, m0 = (tile % tiles_n) * 256, (tile // tiles_n) * 256
+        same = np.array_equal(a[m0:m0 + 256, n0:n0 + 256], b[m0:m0 + 256, n0:n0 + 256])
+        if tile < full:
+            assert same, tile
+        else:
+            differs += not same
+    assert differs > 0      # the split path really ran
