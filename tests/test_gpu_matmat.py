@@ -159,11 +159,11 @@ def test_pair_kernel_equals_single_cta_kernel(tmp_path, monkeypatch, dt, M):
 
 
 @pytest.mark.parametrize("dt", [oc.Q8_ROW, oc.Q4_TILED, oc.Q4TP])
-@pytest.mark.parametrize("M,K,N", [(4352, 2304, 9216), (2700, 2304, 9216), (8704, 9216, 2304), (8704, 2304, 2304)])
+@pytest.mark.parametrize("M,K,N", [(8704, 9216, 2304), (4352, 4096, 4608), (2700, 8192, 2304)])
 def test_pair_kernel_k_split_of_last_wave(tmp_path, monkeypatch, dt, M, K, N):
-    """These shapes leave a last wave of tiles that fills less than half of the 74 CTA pairs (20, 26,
-    10 and 10 tiles); the kernel cuts those tiles along K into slices for all pairs and a second
-    kernel adds the slices in order.  Same result as the unsplit kernel up to the f32 summation
+    """These shapes (K of 4096 or more) leave a last wave of tiles that fills less than half of the 74
+    CTA pairs (10, 10 and 25 tiles); the kernel cuts those tiles along K into slices for all pairs and a
+    second kernel adds the slices in order.  Same result as the unsplit kernel up to the f32 summation
     order, identical from run to run, and every tile outside the last wave bit-identical."""
     from cmf_b200 import Model, gpu
     rng = np.random.default_rng(5)
