@@ -579,8 +579,11 @@ int dev_gemm(Context* c, DevWeight* w, const __nv_bfloat16* x, int M, void* out,
     p.out = out; p.ldo = ldo; p.mode = mode;
     p.row_scale = w->dtype == DT_Q8 ? w->scales : nullptr;
     p.status = c->status;
-    const char* split_env = getenv("CMFC_GEMM_SPLITK");  // "0": never cut a last partial wave along K
-    p.splitk_ws = (split_env && split_env[0] == '0') ? nullptr : c->splitk_ws;
+    // Cutting a last partial wave along K is opt-in (CMFC_GEMM_SPLITK=1): which tiles are cut depends
+    // on the token count, so with it on a prompt's result depends (in the last f32 bits of a GEMM,
+    // then through bf16 rounding flips) on what else is in its batch.
+    const char* split_env = getenv("CMFC_GEMM_SPLITK");
+    p.splitk_ws = (split_env && split_env[0] == '1') ? c->splitk_ws : nullptr;
     const int wkind = w->dtype == DT_Q8 ? 0 : (w->dtype == DT_Q4TP ? 1 : 2);
     // CTA-pair kernel (2-SM MMA) whenever the weight rows tile by 256 and there is at least one
     // tile per pair of SMs; otherwise the single-CTA kernel.  CMFC_GEMM_PAIR=0 forces the latter.
