@@ -79,6 +79,10 @@ SYMBOLS = {
                                C.c_void_p, C.c_size_t, C.c_uint32, C.c_float]),
     "cmfc_denoise_begin": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p,
                                      C.c_size_t, C.c_void_p, C.c_size_t, C.c_uint32, C.c_float]),
+    "cmfc_denoise_ex": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p, C.c_size_t,
+                                  C.c_void_p, C.c_size_t, C.c_void_p]),
+    "cmfc_denoise_begin_ex": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p,
+                                        C.c_size_t, C.c_void_p, C.c_size_t, C.c_void_p]),
     "cmfc_denoise_step": (C.c_int, [C.c_void_p, C.c_uint32]),
     "cmfc_denoise_end": (C.c_int, [C.c_void_p, C.c_void_p]),
     "cmfc_payload_nbytes": (C.c_size_t, [C.c_int, C.c_size_t, C.c_size_t]),
@@ -86,6 +90,7 @@ SYMBOLS = {
     "cmfc_encode_random": (C.c_int, [C.c_int, C.c_uint64, C.c_float, C.c_size_t, C.c_size_t, C.c_void_p]),
     "cmfc_noalloc_max_elements": (C.c_size_t, []),
     "cmfc_matmat_device_noalloc": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "cmfc_selftest_wait_timeout": (C.c_int, [C.c_uint32]),
     "cmfc_launch_count": (C.c_uint64, [C.c_int]),
     "cmfc_bench_gemm": (C.c_int, [C.c_void_p, C.c_int64, C.c_size_t, C.c_int, C.c_int, C.POINTER(C.c_float)]),
     "cmfc_bench_attention": (C.c_int, [C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t, C.c_int, C.POINTER(C.c_float)]),

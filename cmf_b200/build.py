@@ -5,7 +5,7 @@ import subprocess
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libcmf_cuda.so")
-SOURCES = ["gemm_dequant.cu", "gemm_dequant_pair.cu", "attention.cu", "rowops.cu", "codec_kernels.cu", "runtime.cu", "api.cu", "noalloc.cu",
+SOURCES = ["gemm_dequant.cu", "gemm_dequant_pair.cu", "attention.cu", "rowops.cu", "codec_kernels.cu", "runtime.cu", "api.cu", "noalloc.cu", "selftest.cu",
            "conv_f16x2.cu", "vae_kernels.cu", "vae.cu", "gemma_kernels.cu", "gemma.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v", "--expt-relaxed-constexpr"]

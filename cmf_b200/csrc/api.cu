@@ -263,8 +263,10 @@ extern "C" int cmfc_dit_block_seg(cmfc_model* m, const cmfc_dit_block_args* a, c
     if ((size_t)bw.qkv->rows != (a->nh + 2 * a->nkv) * (size_t)a->hd || (size_t)bw.qkv->cols != hs || (size_t)bw.w13->rows != 2 * (size_t)a->inter ||
         (size_t)bw.w2->cols != a->inter || (size_t)bw.o->rows != hs)
         return fail(ERR_SHAPE, "dit_block_seg: projection shapes disagree with the block geometry");
-    // rope: f32 twins from the caller, widened to f64 (exact); cached while unchanged
-    static thread_local std::vector<float> rope_cache;
+    // rope: f32 twins from the caller, widened to f64 (exact); re-uploaded only when the caller's
+    // table changes.  The host copy it is compared with belongs to the context, like the device
+    // buffer it describes, so a thread that moves between devices never matches another GPU's table.
+    std::vector<float>& rope_cache = c->facade_rope_host;
     DevBuf& rope = c->buf("facade_rope");
     const size_t rn = n * pairs;
     bool same = rope_cache.size() == 2 * rn && rope.p && !memcmp(rope_cache.data(), a->rope_cos, rn * 4) &&
@@ -272,8 +274,12 @@ extern "C" int cmfc_dit_block_seg(cmfc_model* m, const cmfc_dit_block_args* a, c
     if (!same) {
         std::vector<double> wide(2 * rn);
         for (size_t i = 0; i < rn; ++i) { wide[i] = a->rope_cos[i]; wide[rn + i] = a->rope_sin[i]; }
+        rope_cache.clear();
+        CMFC_CUDA(cudaStreamSynchronize(c->stream));  // an earlier block may still read the old table
         CMFC_TRY(rope.ensure(2 * rn * 8));
-        CMFC_CUDA(cudaMemcpy(rope.p, wide.data(), 2 * rn * 8, cudaMemcpyHostToDevice));
+        // on the stream the readers run on (it is not ordered after the legacy default stream)
+        CMFC_CUDA(cudaMemcpyAsync(rope.p, wide.data(), 2 * rn * 8, cudaMemcpyHostToDevice, c->stream));
+        CMFC_CUDA(cudaStreamSynchronize(c->stream));  // `wide` is a local
         rope_cache.assign(a->rope_cos, a->rope_cos + rn);
         rope_cache.insert(rope_cache.end(), a->rope_sin, a->rope_sin + rn);
     }
@@ -333,23 +339,35 @@ struct cmfc_nextdit {
     const float *x_emb_w = nullptr, *x_emb_b = nullptr, *t1w = nullptr, *t1b = nullptr, *t2w = nullptr, *t2b = nullptr;
     const float *cap_norm = nullptr, *cap_b = nullptr, *out1_w = nullptr, *out1_b = nullptr, *out2_w = nullptr, *out2_b = nullptr;
     DevWeight* cap_w = nullptr;  // quantized (tensor core path) or dense f32
-    // rope tables cached by geometry
-    std::string rope_key;
-    DevBuf rope_joint, rope_img, rope_cap;
+    // rope tables cached by geometry, one set per forward shape (index 0: one sequence per prompt,
+    // 1: the cond/uncond pair), so the two captured step graphs never share a table
+    std::string rope_key[2];
+    DevBuf rope_joint[2], rope_img[2], rope_cap;
+    uint64_t rope_epoch = 0;           // bumped by every table upload: a captured graph reads the tables' contents
     // denoise state
     DevBuf latents, cap_c_r, cap_u_r, pred_c, pred_u;
     size_t batch = 0, lh = 0, lw = 0, cap_n = 0, cap_u_n = 0;
     uint32_t steps = 0;
+    uint32_t cfg_steps = 0;            // steps [0, cfg_steps) run the guided pair, the rest cond only
     float gs = 4.0f;
     bool cfg = false;
+    bool cfg_norm = true;
     std::vector<double> sig;
     uint32_t next_step = 0;            // value of the device step counter
-    // one captured denoise step (all launches of forward + CFG/Euler), replayed by later steps
-    cudaGraphExec_t graph = nullptr;
-    uint64_t graph_epoch = 0;          // allocation epoch at capture time
-    uint64_t graph_launches = 0;       // kernel launches inside the graph
+    // captured denoise steps (all launches of forward + CFG/Euler), replayed by later steps of the
+    // same kind: index 0 = cond-only step, 1 = guided (pair) step
+    struct StepGraph {
+        cudaGraphExec_t exec = nullptr;
+        uint64_t alloc_epoch = 0;      // allocation epoch at capture time
+        uint64_t rope_epoch = 0;       // rope-table epoch at capture time
+        uint64_t launches = 0;         // kernel launches inside the graph
+        int eager_steps = 0;           // steps of this kind run eagerly since the last begin (the first warms buffers)
+        void drop() {
+            if (exec) cudaGraphExecDestroy(exec);
+            exec = nullptr;
+        }
+    } graphs[2];
     std::string graph_key;
-    int eager_steps = 0;               // steps run eagerly since the last begin (the first one warms buffers)
 };
 
 namespace {
@@ -480,8 +498,10 @@ int upload_rope(Context* c, DevBuf* buf, const std::vector<int>& ids3, const int
     // kernels already queued on the stream may still read the previous table
     CMFC_CUDA(cudaStreamSynchronize(c->stream));
     CMFC_TRY(buf->ensure(cs.size() * 16));
-    CMFC_CUDA(cudaMemcpy(buf->p, cs.data(), cs.size() * 8, cudaMemcpyHostToDevice));
-    CMFC_CUDA(cudaMemcpy(buf->as<double>() + cs.size(), sn.data(), sn.size() * 8, cudaMemcpyHostToDevice));
+    // on the stream the readers run on (it is not ordered after the legacy default stream)
+    CMFC_CUDA(cudaMemcpyAsync(buf->p, cs.data(), cs.size() * 8, cudaMemcpyHostToDevice, c->stream));
+    CMFC_CUDA(cudaMemcpyAsync(buf->as<double>() + cs.size(), sn.data(), sn.size() * 8, cudaMemcpyHostToDevice, c->stream));
+    CMFC_CUDA(cudaStreamSynchronize(c->stream));  // cs / sn are locals
     return OK;
 }
 void push_ids(std::vector<int>* v, int a, int b, int cc) { v->push_back(a); v->push_back(b); v->push_back(cc); }
@@ -616,7 +636,9 @@ int forward_device(Context* c, cmfc_nextdit* d, const float* latents, int batch,
     int n_joint = 0;
     for (int b = 0; b < batch; ++b)
         for (int q = 0; q < nseq; ++q) { segs_joint.push_back(cap_ns[q] + n_img); n_joint += cap_ns[q] + n_img; }
-    if (d->rope_key != key.str()) {
+    const int rs = nseq > 1 ? 1 : 0;
+    DevBuf &rope_img = d->rope_img[rs], &rope_joint = d->rope_joint[rs];
+    if (d->rope_key[rs] != key.str()) {
         std::vector<int> ids_img, ids_joint;
         // refiner image ids: axis 0 is 0 in the pair path and cap_n in the single path
         // (crates/cortiq-engine/src/dit.rs:1287-1292 vs :1431-1435)
@@ -628,14 +650,16 @@ int forward_device(Context* c, cmfc_nextdit* d, const float* latents, int batch,
                 for (int i = 0; i < cap_ns[q]; ++i) push_ids(&ids_joint, i, 0, 0);
                 for (int i = 0; i < n_img; ++i) push_ids(&ids_joint, cap_ns[q], i / wp, i % wp);
             }
-        CMFC_TRY(upload_rope(c, &d->rope_img, ids_img, d->axes));
-        CMFC_TRY(upload_rope(c, &d->rope_joint, ids_joint, d->axes));
-        d->rope_key = key.str();
+        d->rope_key[rs].clear();
+        d->rope_epoch++;
+        CMFC_TRY(upload_rope(c, &rope_img, ids_img, d->axes));
+        CMFC_TRY(upload_rope(c, &rope_joint, ids_joint, d->axes));
+        d->rope_key[rs] = key.str();
     }
     size_t mk = 0;
     for (size_t l = 0; l < d->noise_ref.size(); ++l, ++mk) {
         const DitBlock* nx = l + 1 < d->noise_ref.size() ? &d->noise_ref[l + 1] : nullptr;
-        CMFC_TRY(run_block(c, d, d->noise_ref[l], img.as<float>(), batch * n_img, segs_img, mods + mk * 4 * hs, d->rope_img,
+        CMFC_TRY(run_block(c, d, d->noise_ref[l], img.as<float>(), batch * n_img, segs_img, mods + mk * 4 * hs, rope_img,
                            (size_t)batch * n_img, nx, mods + (mk + 1) * 4 * hs, l > 0));
     }
     // ---- joint sequences: [cap | img] per (prompt, branch) ----
@@ -654,7 +678,7 @@ int forward_device(Context* c, cmfc_nextdit* d, const float* latents, int batch,
     }
     for (size_t l = 0; l < d->layers.size(); ++l) {
         const DitBlock* nx = l + 1 < d->layers.size() ? &d->layers[l + 1] : nullptr;
-        CMFC_TRY(run_block(c, d, d->layers[l], xb.as<float>(), n_joint, segs_joint, mods + mk * 4 * hs, d->rope_joint, (size_t)n_joint,
+        CMFC_TRY(run_block(c, d, d->layers[l], xb.as<float>(), n_joint, segs_joint, mods + mk * 4 * hs, rope_joint, (size_t)n_joint,
                            nx, mods + (mk + 1) * 4 * hs, l > 0));
         ++mk;
         if (taps) CMFC_CUDA(cudaMemcpyAsync(taps + l * (size_t)n_joint * hs, xb.p, (size_t)n_joint * hs * 4, cudaMemcpyDeviceToDevice, s));
@@ -748,7 +772,10 @@ extern "C" int cmfc_nextdit_create(cmfc_model* mm, cmfc_nextdit** out) {
 
 extern "C" void cmfc_nextdit_destroy(cmfc_nextdit* d) {
     if (!d) return;
-    for (DevBuf* b : {&d->rope_joint, &d->rope_img, &d->rope_cap, &d->latents, &d->cap_c_r, &d->cap_u_r, &d->pred_c, &d->pred_u}) b->release();
+    for (auto& g : d->graphs) g.drop();
+    for (DevBuf* b : {&d->rope_joint[0], &d->rope_joint[1], &d->rope_img[0], &d->rope_img[1], &d->rope_cap, &d->latents, &d->cap_c_r,
+                      &d->cap_u_r, &d->pred_c, &d->pred_u})
+        b->release();
     delete d;
 }
 
@@ -822,15 +849,25 @@ extern "C" int cmfc_nextdit_forward_pair_taps(cmfc_nextdit* d, const float* late
 }
 
 // ---------------- Euler loop ----------------
-extern "C" int cmfc_denoise_begin(cmfc_nextdit* d, const float* latents, size_t batch, size_t h, size_t w, const float* cap,
-                                  size_t cap_n, const float* cap_u, size_t cap_u_n, uint32_t steps, float guidance_scale) {
-    NEED(d && latents && cap && batch > 0 && cap_n > 0 && steps > 0, "denoise: null argument or empty input");
+extern "C" int cmfc_denoise_begin_ex(cmfc_nextdit* d, const float* latents, size_t batch, size_t h, size_t w, const float* cap,
+                                     size_t cap_n, const float* cap_u, size_t cap_u_n, const cmfc_gen_params* gp) {
+    NEED(d && latents && cap && gp && batch > 0 && cap_n > 0 && gp->steps > 0, "denoise: null argument or empty input");
+    NEED(gp->cfg_trunc_ratio == gp->cfg_trunc_ratio, "denoise: cfg_trunc_ratio is NaN");
     NEED_CTX();
+    const uint32_t steps = gp->steps;
+    const float guidance_scale = gp->guidance_scale;
     const size_t lat_n = batch * d->ch * h * w, hs = d->hidden, cf = d->cap_feat;
     d->batch = batch; d->lh = h; d->lw = w; d->cap_n = cap_n; d->cap_u_n = cap_u ? cap_u_n : 0; d->steps = steps;
     d->gs = guidance_scale;
     d->cfg = cap_u != nullptr;
+    d->cfg_norm = gp->cfg_normalization != 0;
     NEED(!d->cfg || cap_u_n > 0, "denoise: empty uncond caption");
+    // CFG truncation (crates/cortiq-engine/src/imagegen.rs:164): step i is guided while
+    // (i + 1) / steps <= cfg_trunc_ratio, evaluated in f32 like the engine; past it only cond runs
+    d->cfg_steps = 0;
+    if (d->cfg)
+        for (uint32_t i = 0; i < steps; ++i)
+            if ((float)(i + 1) / (float)steps <= gp->cfg_trunc_ratio) d->cfg_steps = i + 1;
     // sigma schedule (crates/cortiq-engine/src/imagegen.rs:59-73), shift 6
     d->sig.clear();
     for (uint32_t i = 0; i < steps; ++i) {
@@ -861,26 +898,31 @@ extern "C" int cmfc_denoise_begin(cmfc_nextdit* d, const float* latents, size_t 
     }
     CMFC_TRY(upload_schedule(c, td, 0));
     d->next_step = 0;
-    d->eager_steps = 0;
     std::ostringstream key;
-    key << batch << ":" << h << ":" << w << ":" << cap_n << ":" << d->cap_u_n << ":" << guidance_scale;
-    if (d->graph && key.str() != d->graph_key) {
-        cudaGraphExecDestroy(d->graph);
-        d->graph = nullptr;
+    key << batch << ":" << h << ":" << w << ":" << cap_n << ":" << d->cap_u_n << ":" << guidance_scale << ":" << (int)d->cfg_norm;
+    for (auto& g : d->graphs) {
+        g.eager_steps = 0;
+        if (key.str() != d->graph_key) g.drop();
     }
     d->graph_key = key.str();
     return OK;
 }
 
+extern "C" int cmfc_denoise_begin(cmfc_nextdit* d, const float* latents, size_t batch, size_t h, size_t w, const float* cap,
+                                  size_t cap_n, const float* cap_u, size_t cap_u_n, uint32_t steps, float guidance_scale) {
+    const cmfc_gen_params gp = {steps, guidance_scale, 1.0f, 1};
+    return cmfc_denoise_begin_ex(d, latents, batch, h, w, cap, cap_n, cap_u, cap_u_n, &gp);
+}
+
 namespace {
 // every launch of one denoise step, in stream order
-int enqueue_step(Context* c, cmfc_nextdit* d) {
+int enqueue_step(Context* c, cmfc_nextdit* d, bool guided) {
     const float* caps[2] = {d->cap_c_r.as<float>(), d->cap_u_r.as<float>()};
     const int cap_ns[2] = {(int)d->cap_n, (int)d->cap_u_n};
     float* preds[2] = {d->pred_c.as<float>(), d->pred_u.as<float>()};
-    CMFC_TRY(forward_device(c, d, d->latents.as<float>(), (int)d->batch, (int)d->lh, (int)d->lw, d->cfg ? 2 : 1, caps, cap_ns, 0.0f, preds, nullptr));
+    CMFC_TRY(forward_device(c, d, d->latents.as<float>(), (int)d->batch, (int)d->lh, (int)d->lw, guided ? 2 : 1, caps, cap_ns, 0.0f, preds, nullptr));
     launch_cfg_euler(d->latents.as<float>(), d->pred_c.as<float>(), d->pred_u.as<float>(), d->gs, c->sched, c->step_counter,
-                     (int)(d->batch * d->ch * d->lh), (int)d->lw, d->cfg ? 1 : 0, c->stream);
+                     (int)(d->batch * d->ch * d->lh), (int)d->lw, guided ? (d->cfg_norm ? 1 : 2) : 0, c->stream);
     launch_advance_step(c->step_counter, c->stream);
     c->launches += 2;
     CMFC_CUDA(cudaGetLastError());
@@ -897,45 +939,47 @@ extern "C" int cmfc_denoise_step(cmfc_nextdit* d, uint32_t i) {
         CMFC_CUDA(cudaMemcpyAsync(c->step_counter, c->sched_host + 2 * Context::MAX_STEPS, 4, cudaMemcpyHostToDevice, c->stream));
     }
     d->next_step = i + 1;
-    // The step's ~320 launches are captured once into a CUDA graph and replayed: the timestep and
-    // step size come from the device-resident schedule, so nothing in the graph depends on i.  The
-    // first step after begin runs eagerly (it may grow workspaces and upload tables); profiling
-    // spans need eager launches too.
-    static const bool graphs_on = !(getenv("CMFC_GRAPH") && atoi(getenv("CMFC_GRAPH")) == 0);
-    if (d->graph && d->graph_epoch != alloc_epoch()) {
-        cudaGraphExecDestroy(d->graph);
-        d->graph = nullptr;
-    }
-    if (graphs_on && !c->prof.on && d->graph) {
-        CMFC_CUDA(cudaGraphLaunch(d->graph, c->stream));
-        c->launches += d->graph_launches;
+    // The step's launches (about 470 for the 30-block pair forward) are captured once into a CUDA
+    // graph and replayed: the timestep and step size come from the device-resident schedule, so
+    // nothing in the graph depends on i.  Guided and cond-only steps (CFG truncation) are different
+    // graphs.  The first step of a kind after begin runs eagerly (it may grow workspaces and upload
+    // tables); profiling spans need eager launches too.
+    const bool guided = d->cfg && i < d->cfg_steps;
+    cmfc_nextdit::StepGraph& sg = d->graphs[guided ? 1 : 0];
+    const char* graph_env = getenv("CMFC_GRAPH");  // read per call, like the other switches
+    const bool graphs_on = !(graph_env && atoi(graph_env) == 0);
+    if (sg.exec && (sg.alloc_epoch != alloc_epoch() || sg.rope_epoch != d->rope_epoch)) sg.drop();
+    if (graphs_on && !c->prof.on && sg.exec) {
+        CMFC_CUDA(cudaGraphLaunch(sg.exec, c->stream));
+        c->launches += sg.launches;
         return OK;
     }
-    if (graphs_on && !c->prof.on && d->eager_steps >= 1) {
-        const uint64_t before = c->launches, epoch = alloc_epoch();
+    if (graphs_on && !c->prof.on && sg.eager_steps >= 1) {
+        const uint64_t before = c->launches, epoch = alloc_epoch(), repoch = d->rope_epoch;
         cudaGraph_t g = nullptr;
         CMFC_CUDA(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
-        const int rc = enqueue_step(c, d);
+        const int rc = enqueue_step(c, d, guided);
         const cudaError_t ce = cudaStreamEndCapture(c->stream, &g);
-        if (rc == OK && ce == cudaSuccess && g && epoch == alloc_epoch() &&
-            cudaGraphInstantiate(&d->graph, g, 0) == cudaSuccess) {
-            d->graph_launches = c->launches - before;
+        if (rc == OK && ce == cudaSuccess && g && epoch == alloc_epoch() && repoch == d->rope_epoch &&
+            cudaGraphInstantiate(&sg.exec, g, 0) == cudaSuccess) {
+            sg.launches = c->launches - before;
             c->launches = before;
-            d->graph_epoch = epoch;
+            sg.alloc_epoch = epoch;
+            sg.rope_epoch = repoch;
             cudaGraphDestroy(g);
-            CMFC_CUDA(cudaGraphLaunch(d->graph, c->stream));
-            c->launches += d->graph_launches;
+            CMFC_CUDA(cudaGraphLaunch(sg.exec, c->stream));
+            c->launches += sg.launches;
             return OK;
         }
         // capture did not work out (e.g. a workspace had to grow): nothing ran; fall through to eager
         if (g) cudaGraphDestroy(g);
-        d->graph = nullptr;
+        sg.exec = nullptr;
         c->launches = before;
         cudaGetLastError();
         if (rc != OK) return rc;
     }
-    d->eager_steps++;
-    return enqueue_step(c, d);
+    sg.eager_steps++;
+    return enqueue_step(c, d, guided);
 }
 
 extern "C" int cmfc_denoise_end(cmfc_nextdit* d, float* latents) {
@@ -945,11 +989,17 @@ extern "C" int cmfc_denoise_end(cmfc_nextdit* d, float* latents) {
     return check_status(c, "denoise");
 }
 
+extern "C" int cmfc_denoise_ex(cmfc_nextdit* d, float* latents, size_t batch, size_t h, size_t w, const float* cap, size_t cap_n,
+                               const float* cap_u, size_t cap_u_n, const cmfc_gen_params* gp) {
+    CMFC_TRY(cmfc_denoise_begin_ex(d, latents, batch, h, w, cap, cap_n, cap_u, cap_u_n, gp));
+    for (uint32_t i = 0; i < gp->steps; ++i) CMFC_TRY(cmfc_denoise_step(d, i));
+    return cmfc_denoise_end(d, latents);
+}
+
 extern "C" int cmfc_denoise(cmfc_nextdit* d, float* latents, size_t batch, size_t h, size_t w, const float* cap, size_t cap_n,
                             const float* cap_u, size_t cap_u_n, uint32_t steps, float guidance_scale) {
-    CMFC_TRY(cmfc_denoise_begin(d, latents, batch, h, w, cap, cap_n, cap_u, cap_u_n, steps, guidance_scale));
-    for (uint32_t i = 0; i < steps; ++i) CMFC_TRY(cmfc_denoise_step(d, i));
-    return cmfc_denoise_end(d, latents);
+    const cmfc_gen_params gp = {steps, guidance_scale, 1.0f, 1};
+    return cmfc_denoise_ex(d, latents, batch, h, w, cap, cap_n, cap_u, cap_u_n, &gp);
 }
 
 // ---------------- quantizers ----------------

@@ -27,6 +27,8 @@
 // S(j) into registers and is ready long before they need it: a tile never waits for the tensor
 // pipe, only for the shared P buffer, which the other tile's P V frees half a period earlier.
 // head_dim 128 does not fit that plan (O needs 2 x 128 columns) and keeps P over S.
+#include <atomic>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -410,7 +412,7 @@ int attn_smem_bytes(int hd) {
 template <int HD, int POLY>
 static int launch_hd(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_vt, const AttnParams& p,
                      cudaStream_t stream) {
-    static bool configured[64] = {false};  // per instantiation and device; never repeated inside a stream capture
+    static std::atomic<bool> configured[64];  // per instantiation and device; never repeated inside a stream capture
     int dev = 0;
     CMFC_CUDA(cudaGetDevice(&dev));
     if (!configured[dev & 63]) {

@@ -125,10 +125,9 @@ __device__ __forceinline__ bool mbar_try_parked(uint64_t* bar, uint32_t parity, 
 // leaves the issue slots of its scheduler to the warps doing the work.  The budget is about two
 // seconds either way.
 template <uint32_t NAP_NS = 0>
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                          uint32_t site) {
+__device__ __forceinline__ bool mbar_wait_budget(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                                 uint32_t site, uint32_t polls) {
     if (mbar_try(bar, parity)) return true;
-    constexpr uint32_t polls = NAP_NS ? (2000000000u / (NAP_NS + 200u)) : WAIT_POLLS;
     for (uint32_t i = 0; i < polls; ++i) {
         if (NAP_NS) __nanosleep(NAP_NS);
         if (NAP_NS ? mbar_try(bar, parity) : mbar_try_parked(bar, parity, WAIT_PARK_NS)) return true;
@@ -136,6 +135,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     }
     atomicCAS(const_cast<uint32_t*>(abort_flag), 0u, site);
     return false;
+}
+template <uint32_t NAP_NS = 0>
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                          uint32_t site) {
+    constexpr uint32_t polls = NAP_NS ? (2000000000u / (NAP_NS + 200u)) : WAIT_POLLS;
+    return mbar_wait_budget<NAP_NS>(bar, parity, abort_flag, site, polls);
 }
 
 // ---- TMA (tiled, no multicast) ----

@@ -22,6 +22,8 @@
 // channel-major ([oc][pixel]: NCHW, also V^T of the attention block).  Every wait is bounded.
 #include <cuda_fp16.h>
 
+#include <atomic>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -276,7 +278,7 @@ int launch_conv_f16x2(const CUtensorMap& tm_a_hi, const CUtensorMap& tm_a_lo, co
     if (p.a_planes < 1 || p.a_planes > 2 || p.b_planes < 1 || p.b_planes > 2)
         return fail(ERR_BAD_ARG, "conv: operand planes must be 1 or 2");
     if (p.oc <= 0 || p.w <= 0 || p.h <= 0) return fail(ERR_SHAPE, "conv: empty output");
-    static bool configured[64] = {false};
+    static std::atomic<bool> configured[64];
     int dev = 0;
     CMFC_CUDA(cudaGetDevice(&dev));
     if (!configured[dev & 63]) {

@@ -21,6 +21,8 @@
 //
 // bf16 operand definition: RN_bf16(exact f32 dequantized weight).  For q8 the integer level
 // itself is the operand (exact in bf16) and the f32 row scale is applied to the accumulator.
+#include <atomic>
+
 #include "common.cuh"
 #include "gemm_unpack.cuh"
 #include "kernels.h"
@@ -335,7 +337,7 @@ int launch_gemm_dequant(int wkind, const CUtensorMap& tm_x, const CUtensorMap& t
                         const GemmParams& p, int num_sms, cudaStream_t stream) {
     if (p.K % BK != 0 || p.N % TW != 0 || p.M <= 0)
         return fail(ERR_SHAPE, "dequant GEMM needs K % 64 == 0 and N % 128 == 0");
-    static bool configured[3][64] = {};  // per codec kernel and device
+    static std::atomic<bool> configured[3][64];  // per codec kernel and device
     auto kern = wkind == 0 ? gemm_dequant_kernel<0> : (wkind == 1 ? gemm_dequant_kernel<1> : gemm_dequant_kernel<2>);
     int dev = 0;
     CMFC_CUDA(cudaGetDevice(&dev));

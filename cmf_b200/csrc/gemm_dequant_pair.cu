@@ -16,6 +16,8 @@
 #include <cooperative_groups.h>
 #include <algorithm>
 
+#include <atomic>
+
 #include "common.cuh"
 #include "gemm_unpack.cuh"
 #include "kernels.h"
@@ -404,7 +406,7 @@ int gemm_pair_tile_tokens() { return TH; }
 int launch_gemm_dequant_pair(int wkind, const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUtensorMap& tm_s,
                              const GemmParams& p, int num_sms, cudaStream_t stream) {
     if (!gemm_pair_supported(p)) return fail(ERR_SHAPE, "pair GEMM needs K % 64 == 0 and N % 256 == 0");
-    static bool configured[3][64] = {};
+    static std::atomic<bool> configured[3][64];
     auto kern = wkind == 0 ? gemm_dequant_pair_kernel<0> : (wkind == 1 ? gemm_dequant_pair_kernel<1> : gemm_dequant_pair_kernel<2>);
     int dev = 0;
     CMFC_CUDA(cudaGetDevice(&dev));

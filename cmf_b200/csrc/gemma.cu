@@ -92,6 +92,7 @@ int load_norm_plus_one(Context* c, cmfc_gemma* g, const std::string& name, int e
     if (cudaMalloc(&d, n * 4) != cudaSuccess) return fail(ERR_OOM, "out of device memory for a norm weight");
     g->owned.push_back(d);
     CMFC_CUDA(cudaMemcpy(d, v.data(), n * 4, cudaMemcpyHostToDevice));
+    CMFC_CUDA(cudaStreamSynchronize(0));  // readers run on a stream that is not ordered after the legacy one
     *out = reinterpret_cast<float*>(d);
     return OK;
 }

@@ -3,6 +3,8 @@
 // half-split RoPE in f32 (:271-286), causal soft-capped attention in f32 (:287-323).
 // A prompt is at most a few hundred tokens: these are small exact-f32 kernels; the projections
 // go through the dequant GEMM.
+#include <atomic>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -240,7 +242,7 @@ int launch_attn_causal_f32(const float* qkv, int n, int nh, int nkv, int hd, flo
     const int s_pitch = ((n + 31) / 32) * 32 + 1;
     const size_t smem = sizeof(float) * ((size_t)GQ * hd + (size_t)GQ * (hd + 1) + (size_t)GQ * s_pitch);
     if (smem > 200 * 1024) return fail(ERR_UNSUPPORTED, "causal attention: prompt too long for the score tile in shared memory");
-    static bool configured[64] = {false};
+    static std::atomic<bool> configured[64];
     int dev = 0;
     CMFC_CUDA(cudaGetDevice(&dev));
     if (!configured[dev & 63]) {

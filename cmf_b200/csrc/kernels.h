@@ -112,6 +112,7 @@ void launch_layernorm_scale(const float* x, const float* scale, int rows, int co
 void launch_silu_mul(const __nv_bfloat16* gu, int rows, int inter, __nv_bfloat16* out, cudaStream_t s);
 // CFG combine with per-row norm rescale, then Euler update: x -= d * pred
 // schedule: sched[2*i] = timestep t_i, sched[2*i+1] = sigma_{i+1} - sigma_i; *counter = current step
+// use_cfg: 0 x -= d * cond; 1 guided prediction rescaled per row to the cond norm; 2 guided, no rescale
 void launch_cfg_euler(float* latents, const float* cond, const float* uncond, float gs, const float* sched,
                       const int* counter, int rows, int lw, int use_cfg, cudaStream_t s);
 void launch_transpose_head_major(const float* src_head_major, int heads, int n, int hd, float scale,

@@ -428,11 +428,13 @@ cfg_euler_kernel(float* __restrict__ latents, const float* __restrict__ cond, co
     }
     cn = sqrtf(warp_sum(cn));
     gn = sqrtf(warp_sum(gn));
-    const float f = gn > 0.0f ? cn / gn : 1.0f;
+    // use_cfg 1: rescale the guided row to the cond row's norm; 2: guidance without the rescale
+    const bool rescale = use_cfg == 1 && gn > 0.0f;
+    const float f = rescale ? cn / gn : 1.0f;
     for (int c = lane; c < lw; c += 32) {
         const float cv = cond[base + c], uv = uncond[base + c];
         float g = uv + gs * (cv - uv);
-        if (gn > 0.0f) g *= f;
+        if (rescale) g *= f;
         latents[base + c] -= d * g;
     }
 }

@@ -113,7 +113,9 @@ void DevBuf::release() {
 
 // ---------------- contexts ----------------
 static std::mutex g_ctx_mu;
-static std::map<int, std::unique_ptr<Context>> g_ctxs;
+// never destroyed: at process exit the CUDA runtime may already be gone, and the contexts' device
+// memory goes with the process anyway
+static std::map<int, std::unique_ptr<Context>>& g_ctxs = *new std::map<int, std::unique_ptr<Context>>();
 static thread_local int g_cur_device = -1;
 
 int ctx_set_device(int device) {
@@ -163,6 +165,7 @@ int ctx_set_device(int device) {
         CMFC_CUDA(cudaMalloc(&c->exp2_lut, 65536 * 4));
         CMFC_CUDA(cudaMemcpy(c->log2_lut, l2.data(), 65536 * 4, cudaMemcpyHostToDevice));
         CMFC_CUDA(cudaMemcpy(c->exp2_lut, e2.data(), 65536 * 4, cudaMemcpyHostToDevice));
+        CMFC_CUDA(cudaStreamSynchronize(0));  // readers run on c->stream, not ordered after the legacy stream
         g_ctxs[device] = std::move(c);
     }
     g_cur_device = device;
@@ -280,12 +283,17 @@ int model_open(const char* path, Model** out) {
     };
     if (memcmp(b, "CMF\x01", 4) != 0) return bad("bad magic");
     if (rd<uint32_t>(b + 4) != 2) return bad("unsupported container version");
+    // Only bit 0 (the tensor directory) is implemented here; a file that REQUIRES binary masks
+    // (bit 1) or the two-factor quantization (bit 2) must be refused, not run with them ignored
+    // (crates/cortiq-core/src/format.rs:700-712 refuses what it does not understand).
     const uint32_t required = rd<uint32_t>(b + 12);
-    if (required & ~0x7u) return bad("unknown required feature bits");
+    if (required & ~0x1u) return bad("required feature bits " + std::to_string(required) + " are not supported by this backend");
     const uint64_t hdr_off = rd<uint64_t>(b + 0x10), hdr_len = rd<uint64_t>(b + 0x18);
     const uint64_t dir_off = rd<uint64_t>(b + 0x20), dir_len = rd<uint64_t>(b + 0x28);
     const uint64_t data_off = rd<uint64_t>(b + 0x30), data_len = rd<uint64_t>(b + 0x38);
-    if (hdr_off + hdr_len > len || dir_off + dir_len > len || data_off + data_len > len || dir_len < 16)
+    // offsets and lengths come from an untrusted file: compare without forming off + len, which wraps
+    auto inside = [](uint64_t off, uint64_t n, uint64_t total) { return n <= total && off <= total - n; };
+    if (!inside(hdr_off, hdr_len, len) || !inside(dir_off, dir_len, len) || !inside(data_off, data_len, len) || dir_len < 16)
         return bad("section outside the file");
     if (data_off % 4096) return bad("data section is not 4096-aligned");
     if (rd<uint64_t>(b + 0x70) != hash64(b + hdr_off, hdr_len)) return bad("header hash mismatch");
@@ -293,7 +301,7 @@ int model_open(const char* path, Model** out) {
     if (dir_hash && dir_hash != hash64(b + dir_off, dir_len)) return bad("directory hash mismatch");
     const uint8_t* d = b + dir_off;
     const uint64_t count = rd<uint64_t>(d), pool_off = rd<uint64_t>(d + 8);
-    if (16 + count * 56 > dir_len || pool_off > dir_len) return bad("directory records overrun the section");
+    if (count > (dir_len - 16) / 56 || pool_off > dir_len) return bad("directory records overrun the section");
     std::unique_ptr<Model> m(new Model());
     m->uid = g_next_uid++;
     m->path = path;
@@ -313,10 +321,10 @@ int model_open(const char* path, Model** out) {
         t.off = rd<uint64_t>(r + 32);
         t.nbytes = rd<uint64_t>(r + 40);
         t.hash = rd<uint64_t>(r + 48);
-        if (pool_off + noff + nlen > dir_len) return bad("tensor name outside the name pool");
+        if (!inside((uint64_t)noff, (uint64_t)nlen, dir_len - pool_off)) return bad("tensor name outside the name pool");
         t.name.assign(reinterpret_cast<const char*>(d + pool_off + noff), nlen);
         if (t.off % 64) return bad("tensor " + t.name + " is not 64-byte aligned");
-        if (t.off + t.nbytes > data_len) return bad("tensor " + t.name + " runs past the data section");
+        if (!inside(t.off, t.nbytes, data_len)) return bad("tensor " + t.name + " runs past the data section");
         if (t.ndim == 2) {
             size_t want = payload_nbytes(t.dtype, t.shape[0], t.shape[1]);
             if (want && want != t.nbytes) return bad("tensor " + t.name + ": byte count disagrees with dtype and shape");
@@ -331,22 +339,19 @@ void model_close(Model* m) {
     if (!m) return;
     {
         std::lock_guard<std::mutex> lk(g_ctx_mu);
+        // the caller's current device (torch's, in a one-process multi-GPU host) is left as found
+        int caller_dev = -1;
+        const bool have_dev = cudaGetDevice(&caller_dev) == cudaSuccess;
         for (auto& kv : g_ctxs) {
             Context* c = kv.second.get();
             cudaSetDevice(c->device);
             cudaStreamSynchronize(c->stream);
             for (auto it = c->weights.begin(); it != c->weights.end();) {
-                if (std::get<0>(it->first) == m->uid) {
-                    if (it->second->owns) {
-                        cudaFree(it->second->plane);
-                        cudaFree(it->second->scales);
-                    }
-                    it = c->weights.erase(it);
-                } else {
-                    ++it;
-                }
+                if (std::get<0>(it->first) == m->uid) it = c->weights.erase(it);  // ~DevWeight frees the planes
+                else ++it;
             }
         }
+        if (have_dev) cudaSetDevice(caller_dev);
     }
     munmap(const_cast<uint8_t*>(m->map), m->map_len);
     delete m;
@@ -383,6 +388,15 @@ static int finish_gemm_maps(DevWeight* w) {
     }
     w->gemm_ready = true;
     return OK;
+}
+
+// Planes are freed on the device that is current: weights live in a context's map and are dropped
+// either by model_close (which selects the context's device first) or on a failed upload (the
+// uploading thread's device).
+DevWeight::~DevWeight() {
+    if (!owns) return;
+    if (plane) cudaFree(plane);
+    if (scales) cudaFree(scales);
 }
 
 static int alloc_planes(DevWeight* w) {

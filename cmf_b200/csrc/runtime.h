@@ -62,6 +62,10 @@ struct DevWeight {
     bool owns = true;
     size_t bytes = 0;
     bool is_q4() const { return dtype == DT_Q4T || dtype == DT_Q4TP; }
+    DevWeight() = default;
+    DevWeight(const DevWeight&) = delete;
+    DevWeight& operator=(const DevWeight&) = delete;
+    ~DevWeight();  // frees plane and scales when `owns` (a failed upload must not leak them)
 };
 
 struct SegTable {
@@ -89,6 +93,7 @@ struct Context {
     std::map<std::tuple<uint64_t, int64_t, int64_t, int64_t, int>, std::unique_ptr<DevWeight>> weights;
     std::map<std::string, DevBuf> ws;  // named workspaces
     std::vector<std::pair<SegTable, DevBuf>> seg_cache;  // a few recent segmentations, each with its device table
+    std::vector<float> facade_rope_host;  // the caller's f32 RoPE table that ws["facade_rope"] currently holds
     DevBuf resident_x;                 // hidden state kept between chained dit_block_seg calls
     size_t resident_len = 0;
     float* splitk_ws = nullptr;        // partial sums of the pair GEMM's K slices: one slot per CTA pair

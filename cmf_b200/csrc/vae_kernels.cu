@@ -4,6 +4,8 @@
 // and the NHWC split-f16 planes the convolution kernel reads.
 #include <cuda_fp16.h>
 
+#include <atomic>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -370,7 +372,7 @@ int launch_softmax_rows_split(const float* scores, size_t rows, int cols, size_t
         CMFC_CUDA(cudaGetLastError());
         return OK;
     }
-    static bool configured[64] = {false};
+    static std::atomic<bool> configured[64];
     int dev = 0;
     CMFC_CUDA(cudaGetDevice(&dev));
     if (!configured[dev & 63]) {

@@ -16,13 +16,26 @@ def _f32(a):
 
 @dataclass
 class GenParams:
-    """imagegen.rs:22-55 (the fields this backend uses)."""
+    """imagegen.rs:24-55 (the fields this backend uses), with the engine's defaults."""
     steps: int = 30
     guidance_scale: float = 4.0
+    cfg_trunc_ratio: float = 1.0     # fraction of steps that run with CFG; past it only cond runs
+    cfg_normalization: bool = True   # rescale the guided prediction to the cond-branch norm per row
     seed: int = 42
     height: int = 512
     width: int = 512
     max_tokens: int = 256
+
+
+class _CGenParams(C.Structure):
+    """``cmfc_gen_params`` of include/cmf_cuda.h."""
+    _fields_ = [("steps", C.c_uint32), ("guidance_scale", C.c_float), ("cfg_trunc_ratio", C.c_float),
+                ("cfg_normalization", C.c_int32)]
+
+    @classmethod
+    def of(cls, p, steps=None):
+        return cls(int(p.steps if steps is None else steps), float(p.guidance_scale), float(p.cfg_trunc_ratio),
+                   1 if p.cfg_normalization else 0)
 
 
 class NextDit:
@@ -81,7 +94,9 @@ class NextDit:
         return pc, pu, tp
 
     # ---- batched loop, split form ----
-    def denoise_begin(self, latents, cap, cap_u, steps, guidance_scale):
+    def denoise_begin(self, latents, cap, cap_u, steps, guidance_scale, params=None):
+        """``params`` (a GenParams) carries cfg_trunc_ratio / cfg_normalization; its step count and
+        guidance scale are overridden by the explicit arguments."""
         latents, cap = _f32(latents), _f32(cap)
         b, c, h, w = latents.shape
         cap_n = cap.shape[1]
@@ -90,8 +105,10 @@ class NextDit:
             cap_u = _f32(cap_u)
             cu_p, cu_n = cap_u.ctypes.data, cap_u.shape[1]
         self._shape = latents.shape
-        check(lib().cmfc_denoise_begin(self.handle, latents.ctypes.data, b, h, w, cap.ctypes.data, cap_n, cu_p, cu_n,
-                                       steps, C.c_float(guidance_scale)))
+        gp = _CGenParams.of(params or GenParams(), steps)
+        gp.guidance_scale = float(guidance_scale)
+        check(lib().cmfc_denoise_begin_ex(self.handle, latents.ctypes.data, b, h, w, cap.ctypes.data, cap_n, cu_p, cu_n,
+                                          C.byref(gp)))
 
     def denoise_step(self, i):
         check(lib().cmfc_denoise_step(self.handle, i))
@@ -114,6 +131,7 @@ def denoise(dit: NextDit, latents, cap, cap_u, p: GenParams):
     if cap_u is not None:
         cap_u = _f32(cap_u)
         cu_p, cu_n = cap_u.ctypes.data, cap_u.shape[1]
-    check(lib().cmfc_denoise(dit.handle, latents.ctypes.data, b, h, w, cap.ctypes.data, cap.shape[1], cu_p, cu_n,
-                             p.steps, C.c_float(p.guidance_scale)))
+    gp = _CGenParams.of(p)
+    check(lib().cmfc_denoise_ex(dit.handle, latents.ctypes.data, b, h, w, cap.ctypes.data, cap.shape[1], cu_p, cu_n,
+                                C.byref(gp)))
     return latents

@@ -211,6 +211,12 @@ def matmat_device_noalloc(model: Model, idx: int, d_x_ptr: int, b: int, d_y_ptr:
     return True
 
 
+def selftest_wait_timeout(polls=2048):
+    """Let a bounded device wait run out on purpose (a barrier nobody arrives on): raises
+    CmfCudaError with code -5 (CMFC_ERR_DEVICE_WAIT); the context stays usable."""
+    check(lib().cmfc_selftest_wait_timeout(polls))
+
+
 def launch_count(reset=False):
     return int(lib().cmfc_launch_count(int(reset)))
 

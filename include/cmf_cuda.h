@@ -162,15 +162,32 @@ int cmfc_nextdit_forward_pair_taps(cmfc_nextdit* d, const float* latent, size_t 
  *   latents   [batch, c, h, w]  in: start noise, out: denoised latents
  *   cap       [batch, cap_n, cap_feat]   raw caption features (refined once inside)
  *   cap_u     [batch, cap_u_n, cap_feat] or NULL (no CFG)
- * steps / guidance_scale as GenParams (imagegen.rs:41-55); sigma shift 6.0, CFG normalisation on. */
+ * steps / guidance_scale as GenParams (imagegen.rs:41-55); sigma shift 6.0; cfg_trunc_ratio 1 and
+ * CFG normalisation on, the engine's defaults. */
 int cmfc_denoise(cmfc_nextdit* d, float* latents, size_t batch, size_t h, size_t w, const float* cap, size_t cap_n,
                  const float* cap_u, size_t cap_u_n, uint32_t steps, float guidance_scale);
+
+/* The loop's switches of GenParams (imagegen.rs:24-39).  Step i (0-based) is guided while
+ * (i + 1) / steps <= cfg_trunc_ratio (f32, imagegen.rs:164); later steps run the cond branch alone
+ * through the single-sequence forward (dit.rs:1389-1507), as the engine does.  With
+ * cfg_normalization the guided prediction is rescaled per latent row to the cond branch's norm
+ * (imagegen.rs:192-204); without it the plain u + gs (c - u) is used. */
+typedef struct cmfc_gen_params {
+    uint32_t steps;
+    float guidance_scale;
+    float cfg_trunc_ratio;     /* engine default 1.0 */
+    int32_t cfg_normalization; /* engine default 1 */
+} cmfc_gen_params;
+int cmfc_denoise_ex(cmfc_nextdit* d, float* latents, size_t batch, size_t h, size_t w, const float* cap, size_t cap_n,
+                    const float* cap_u, size_t cap_u_n, const cmfc_gen_params* params);
 
 /* Split form of the loop for benchmarking one step with device-resident state:
  * begin uploads inputs and refines captions; step runs denoise step i (0-based) of `steps`;
  * end copies latents back.  cmfc_denoise == begin + steps x step + end. */
 int cmfc_denoise_begin(cmfc_nextdit* d, const float* latents, size_t batch, size_t h, size_t w, const float* cap,
                        size_t cap_n, const float* cap_u, size_t cap_u_n, uint32_t steps, float guidance_scale);
+int cmfc_denoise_begin_ex(cmfc_nextdit* d, const float* latents, size_t batch, size_t h, size_t w, const float* cap,
+                          size_t cap_n, const float* cap_u, size_t cap_u_n, const cmfc_gen_params* params);
 int cmfc_denoise_step(cmfc_nextdit* d, uint32_t i);
 int cmfc_denoise_end(cmfc_nextdit* d, float* latents);
 
@@ -239,14 +256,26 @@ int cmfc_encode_random(int dtype, uint64_t seed, float std, size_t rows, size_t 
  * calls no cudaMalloc / cudaFree and no allocating library routine.  Preconditions: the thread
  * has a device context (cmfc_set_device) and the tensor is already resident on it (any other
  * entry uploads it; cmfc_weight_is_resident tells) -- otherwise CMFC_ERR_BAD_ARG /
- * CMFC_ERR_NOT_FOUND.  The first call on a device looks up the array's device address; make that
- * call before any stream capture.  All calls on a device share the array and it keeps the last
- * call's contents; nothing in it needs clearing between calls, but two calls overlapping on the
- * GPU would race, so serialize them.  Returns after the result is complete in d_y. */
+ * CMFC_ERR_NOT_FOUND.  The first call on a device looks up the array's device address (and, with
+ * lazy module loading, may make the driver load this library's device image, which takes device
+ * memory once); make that call early, before any stream capture.  All calls on a device share the
+ * array and it keeps the last call's contents; nothing in it needs clearing between calls, but two
+ * calls overlapping on the GPU would race, so serialize them.
+ * Ordering: the work runs on the library's own non-blocking stream (cmfc_stream_handle), which is
+ * ordered after NO other stream, the legacy default stream included.  d_x must therefore be
+ * complete before the call, or the caller records an event after the work that fills d_x and makes
+ * the library's stream wait on it (cudaStreamWaitEvent on cmfc_stream_handle()).  The call returns
+ * after the result is complete in d_y, so no ordering is needed on the way out. */
 size_t cmfc_noalloc_max_elements(void);
 int cmfc_matmat_device_noalloc(cmfc_model* m, int64_t idx, const float* d_x, size_t b, float* d_y);
 
 /* ---- instrumentation ---- */
+/* Exercises the failure path of the bounded device waits (no counterpart in the reference, whose
+ * shaders have no waits): launches a one-block kernel that waits, with a budget of `polls` polls
+ * (1 .. 65536; a poll parks for at most 8 us), on a barrier nobody arrives on.  The kernel gives
+ * up, records the site and exits normally; the call returns CMFC_ERR_DEVICE_WAIT, and the context
+ * remains usable for further calls.  Nothing faults or hangs. */
+int cmfc_selftest_wait_timeout(uint32_t polls);
 /* kernels launched by this library on the current device since the last reset */
 uint64_t cmfc_launch_count(int reset);
 /* Time `iters` back-to-back launches of the dequant GEMM for tensor idx at M tokens with

@@ -333,18 +333,21 @@ def cfg_combine(cond, uncond, gs, lw, normalize=True):
     return comb
 
 
-def denoise(model, latents, h, w, cap, cap_u, steps=30, gs=4.0, on_step=None):
-    """crates/cortiq-engine/src/imagegen.rs:143-217 with cfg_trunc_ratio 1 and CFG normalisation
-    on (its defaults).  ``cap`` / ``cap_u`` are raw caption features; refined once."""
+def denoise(model, latents, h, w, cap, cap_u, steps=30, gs=4.0, on_step=None, cfg_trunc_ratio=1.0,
+            cfg_normalization=True):
+    """crates/cortiq-engine/src/imagegen.rs:143-217.  ``cap`` / ``cap_u`` are raw caption
+    features; refined once.  Step i is guided while (i + 1) / steps <= cfg_trunc_ratio in f32
+    (:164); past it only the cond branch runs, through the single-sequence forward."""
     x = np.asarray(latents, np.float32).copy()
     sg = sigmas(steps)
     cap_r = model.refine_caption(cap)
     cap_u_r = model.refine_caption(cap_u) if cap_u is not None else None
     for i in range(steps):
         t = np.float32(1.0 - sg[i])
-        if cap_u_r is not None:
+        cfg_on = cap_u_r is not None and np.float32(i + 1) / np.float32(steps) <= np.float32(cfg_trunc_ratio)
+        if cfg_on:
             pc, pu = model.forward_cfg_pair(x, h, w, cap_r, cap_u_r, t)
-            pred = cfg_combine(pc, pu, gs, w)
+            pred = cfg_combine(pc, pu, gs, w, normalize=cfg_normalization)
         else:
             pred = model.forward_with_cap(x, h, w, cap_r, t)
         d = np.float32(sg[i + 1] - sg[i])

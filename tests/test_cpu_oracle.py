@@ -234,6 +234,99 @@ def test_container_roundtrip_and_validation(tmp_path):
     assert e.value.code == -7
 
 
+def test_reader_rejects_wrapping_offsets_and_unimplemented_features(tmp_path):
+    """Offsets, lengths and counts of an untrusted file must not wrap the reader's bounds checks
+    (the reference uses checked arithmetic, crates/cortiq-core/src/format.rs:700-712), and a file
+    that REQUIRES a feature this backend does not implement (binary masks, two-factor quantization)
+    is refused instead of being run with the feature ignored."""
+    import struct
+    from cmf_b200 import CmfCudaError, Model
+    from cmf_b200.container import CmfWriter, hash64
+    w = (np.random.default_rng(0).standard_normal((128, 64)) * 0.02).astype(np.float32)
+    wr = CmfWriter(arch={"arch_name": "t", "hidden_size": 64, "num_layers": 1, "vocab_size": 0})
+    wr.add("a.q8", oc.Q8_ROW, w.shape, oc.encode(oc.Q8_ROW, w))
+    wr.add_f32("a.f32", w)
+    path = str(tmp_path / "t.cmf")
+    wr.write(path)
+    raw = bytearray(open(path, "rb").read())
+    with Model(path) as m:
+        assert len(m) == 2
+    dir_off, dir_len = struct.unpack_from("<QQ", raw, 0x20)
+    TOP = (1 << 64) - 8
+
+    def reseal(b):      # a forged directory still carries a matching directory hash
+        struct.pack_into("<Q", b, 0x78, hash64(bytes(b[dir_off:dir_off + dir_len])))
+
+    def mut_env(at, value):
+        def f(b):
+            struct.pack_into("<Q", b, at, value)
+        return f
+
+    def mut_dir(at, fmt, value):
+        def f(b):
+            struct.pack_into(fmt, b, dir_off + at, value)
+            reseal(b)
+        return f
+    cases = [
+        (mut_env(0x10, TOP), "section"),                       # hdr_off + hdr_len wraps
+        (mut_env(0x18, TOP), "section"),                       # hdr_len huge
+        (mut_env(0x20, TOP), "section"),                       # dir_off wraps
+        (mut_env(0x28, (1 << 64) - 1), "section"),             # dir_len huge
+        (mut_env(0x30, TOP - (TOP % 4096)), "section"),        # data_off wraps
+        (mut_env(0x38, (1 << 64) - 1), "section"),             # data_len huge
+        (mut_dir(0, "<Q", (1 << 64) // 56 + 1), "directory"),  # count * 56 wraps to a small number
+        (mut_dir(8, "<Q", (1 << 63)), "directory"),            # pool_off beyond the section
+        (mut_dir(16 + 0, "<I", 0xFFFFFFF0), "name"),           # name_off far past the pool
+        (mut_dir(16 + 32, "<Q", TOP - (TOP % 64)), "data section"),   # tensor off + nbytes wraps
+        (mut_dir(16 + 40, "<Q", (1 << 64) - 64), "data section"),     # tensor nbytes huge
+    ]
+    for k, (mutate, frag) in enumerate(cases):
+        bad = bytearray(raw)
+        mutate(bad)
+        p2 = str(tmp_path / f"bad{k}.cmf")
+        open(p2, "wb").write(bad)
+        with pytest.raises(CmfCudaError) as e:
+            Model(p2)
+        assert e.value.code == -8 and frag in str(e.value), (k, str(e.value))
+    for required in (1 | 2, 1 | 4, 2, 4):   # FEAT_BINARY_MASKS, FEAT_QUANT_2F (format.rs required_features)
+        bad = bytearray(raw)
+        struct.pack_into("<I", bad, 12, required)
+        p2 = str(tmp_path / f"feat{required}.cmf")
+        open(p2, "wb").write(bad)
+        with pytest.raises(CmfCudaError) as e:
+            Model(p2)
+        assert e.value.code == -8 and "feature" in str(e.value)
+
+
+def test_reader_opens_a_container_written_by_the_reference_writer():
+    """tests/golden/container_ref_q8.cmf was produced by the reference's own Python writer
+    (converter/convert_dtgma_to_cmf.py _write_cmf / encode_directory:1095-1116; generator
+    tests/golden/make_container_ref.py).  Its directory starts right after the header JSON (no
+    64-byte rounding), 1-D tensors are f16 and every record carries a tensor hash."""
+    from cmf_b200 import Model
+    from cmf_b200.container import hash64
+    want = np.load(os.path.join(GOLD, "container_ref_q8.npz"))
+    with Model(os.path.join(GOLD, "container_ref_q8.cmf")) as m:
+        assert len(m) == len(want.files)
+        # canonical order of the reference writer: final norm, lm_head, then layers by index
+        assert [m.name(i) for i in range(len(m))] == ["model.norm.weight", "lm_head.weight",
+                                                      "model.layers.0.self_attn.q_proj.weight",
+                                                      "model.layers.1.mlp.down_proj.weight"]
+        for name in want.files:
+            w = want[name]
+            i = m.index(name)
+            dt, shape, nb = m.info(i)
+            raw = np.array(m.tensor_bytes(i), copy=True)
+            assert shape == w.shape
+            if w.ndim == 1:
+                assert dt == 1 and np.array_equal(raw.view(np.float16), w.astype(np.float16))
+            else:
+                # the reference's numpy encode_q8_row and the oracle's restatement emit the same bytes
+                assert dt == oc.Q8_ROW and np.array_equal(raw, oc.encode(oc.Q8_ROW, w))
+                assert np.array_equal(oc.dequant(oc.Q8_ROW, raw, *w.shape), oc.dequant(oc.Q8_ROW, oc.encode(oc.Q8_ROW, w), *w.shape))
+            assert nb == raw.size and hash64(raw.tobytes()) != 0
+
+
 def test_container_is_readable_by_reference_reader(tmp_path):
     """Cross-check the writer with the reference's standalone reader where the reference checkout
     is available (CMF_REFERENCE=<checkout>); elsewhere this is covered by the library's own reader."""
