@@ -44,6 +44,31 @@ def gather_latents(local, n_total, group=None, device=None, dst=0):
     return np.concatenate(parts, 0)
 
 
+def denoise_sharded(dit, latents, cap, cap_u, params, group=None, device=None, denoise_fn=None):
+    """``denoise`` for a batch of prompts split over the ranks of a torch.distributed group.
+
+    Every rank passes the SAME full host arrays (``latents`` [n, c, h, w], ``cap`` [n, cap_n, feat],
+    ``cap_u`` [n, cap_u_n, feat] or None); rank r denoises prompts ``shard_range(n, world, r)`` on
+    its own GPU (a prompt's cond/uncond pair never straddles ranks, so CFG combine and the Euler
+    update of crates/cortiq-engine/src/imagegen.rs:186-205 stay rank-local and nothing is exchanged
+    per step) and one gather brings the final latents to rank 0 in prompt order.  Returns the full
+    [n, c, h, w] array on rank 0 and None on the others; without a process group (or with one
+    rank) it is plain ``denoise``.  ``denoise_fn`` replaces the device loop in host-logic tests."""
+    import torch.distributed as dist
+    if denoise_fn is None:
+        from .dit import denoise as denoise_fn
+    n = latents.shape[0]
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+        return denoise_fn(dit, latents, cap, cap_u, params)
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    lo, hi = shard_range(n, world, rank)
+    if hi > lo:
+        local = denoise_fn(dit, latents[lo:hi], cap[lo:hi], None if cap_u is None else cap_u[lo:hi], params)
+    else:
+        local = np.zeros((0,) + tuple(latents.shape[1:]), np.float32)
+    return gather_latents(np.ascontiguousarray(local, np.float32), n, group=group, device=device)
+
+
 def init_cpu_group(rank, world, port, timeout_s=30.0):
     """gloo process group on 127.0.0.1 (host-side tests of the sharding logic)."""
     import torch.distributed as dist

@@ -37,26 +37,40 @@ def _denoise_shard(lo, hi):
         if hi > lo else np.zeros((0, 16, 8, 8), np.float32)
 
 
-def _worker(rank, world, port, q, absent):
+def _oracle_denoise(dit, lat, cap, cap_u, params):
+    """Stand-in for the device loop with the package's ``denoise`` signature: the CPU oracle."""
+    from oracle import nextdit as nd
+    from tests import synth
+    cfg = dict(synth.TINY, num_layers=1, num_refiner_layers=1)
+    orc = nd.NextDitOracle(synth.make_tensors(cfg, 0), cfg)
+    return np.stack([nd.denoise(orc, lat[i], 8, 8, cap[i], cap_u[i], steps=params["steps"]) for i in range(lat.shape[0])])
+
+
+def _worker(rank, world, port, q, absent, sharded=False):
     try:
         import torch.distributed as dist
-        from cmf_b200.shard import gather_latents, init_cpu_group
+        from cmf_b200.shard import denoise_sharded, gather_latents, init_cpu_group
         if rank in absent:
             return  # this rank never joins: the others must fail cleanly, not hang
         init_cpu_group(rank, world, port, timeout_s=6.0)
-        lo, hi = shard_range(3, world, rank)
-        out = gather_latents(_denoise_shard(lo, hi), 3)
+        if sharded:
+            # the product entry: every rank passes the full batch, the shard is taken inside
+            lat, cap, cap_u = _inputs(3)
+            out = denoise_sharded(None, lat, cap, cap_u, {"steps": 2}, denoise_fn=_oracle_denoise)
+        else:
+            lo, hi = shard_range(3, world, rank)
+            out = gather_latents(_denoise_shard(lo, hi), 3)
         q.put((rank, "ok", out))
         dist.destroy_process_group()
     except Exception as e:  # noqa: BLE001
         q.put((rank, "error", repr(e)))
 
 
-def _run(world, absent=()):
+def _run(world, absent=(), sharded=False):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    ps = [ctx.Process(target=_worker, args=(r, world, port, q, absent)) for r in range(world)]
+    ps = [ctx.Process(target=_worker, args=(r, world, port, q, absent, sharded)) for r in range(world)]
     for p in ps:
         p.start()
     res = {}
@@ -87,6 +101,20 @@ def test_two_ranks_match_single_process():
     want = _denoise_shard(0, 3)
     assert res[0][1].shape == want.shape
     assert np.array_equal(res[0][1], want)  # same arithmetic, ragged split 2 + 1
+
+
+def test_denoise_sharded_two_ranks_match_single_process():
+    res = _run(2, sharded=True)
+    assert res[0][0] == "ok" and res[1][0] == "ok", res
+    assert res[1][1] is None
+    assert np.array_equal(res[0][1], _denoise_shard(0, 3))
+
+
+def test_denoise_sharded_without_a_group_is_plain_denoise():
+    from cmf_b200.shard import denoise_sharded
+    lat, cap, cap_u = _inputs(2)
+    got = denoise_sharded(None, lat, cap, cap_u, {"steps": 1}, denoise_fn=lambda d, a, b, c, p: a * 2.0)
+    assert np.array_equal(got, lat * 2.0)
 
 
 def test_missing_rank_is_an_error_not_a_hang():
