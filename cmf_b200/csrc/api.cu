@@ -263,23 +263,22 @@ extern "C" int cmfc_dit_block_seg(cmfc_model* m, const cmfc_dit_block_args* a, c
     if ((size_t)bw.qkv->rows != (a->nh + 2 * a->nkv) * (size_t)a->hd || (size_t)bw.qkv->cols != hs || (size_t)bw.w13->rows != 2 * (size_t)a->inter ||
         (size_t)bw.w2->cols != a->inter || (size_t)bw.o->rows != hs)
         return fail(ERR_SHAPE, "dit_block_seg: projection shapes disagree with the block geometry");
-    // rope: f32 twins from the caller, widened to f64 (exact); re-uploaded only when the caller's
-    // table changes.  The host copy it is compared with belongs to the context, like the device
-    // buffer it describes, so a thread that moves between devices never matches another GPU's table.
+    // rope: the caller's f32 cos / sin tables as they are; re-uploaded only when they change.  The
+    // host copy they are compared with belongs to the context, like the device buffer it describes,
+    // so a thread that moves between devices never matches another GPU's table.
     std::vector<float>& rope_cache = c->facade_rope_host;
     DevBuf& rope = c->buf("facade_rope");
     const size_t rn = n * pairs;
     bool same = rope_cache.size() == 2 * rn && rope.p && !memcmp(rope_cache.data(), a->rope_cos, rn * 4) &&
                 !memcmp(rope_cache.data() + rn, a->rope_sin, rn * 4);
     if (!same) {
-        std::vector<double> wide(2 * rn);
-        for (size_t i = 0; i < rn; ++i) { wide[i] = a->rope_cos[i]; wide[rn + i] = a->rope_sin[i]; }
         rope_cache.clear();
         CMFC_CUDA(cudaStreamSynchronize(c->stream));  // an earlier block may still read the old table
-        CMFC_TRY(rope.ensure(2 * rn * 8));
+        CMFC_TRY(rope.ensure(2 * rn * 4));
         // on the stream the readers run on (it is not ordered after the legacy default stream)
-        CMFC_CUDA(cudaMemcpyAsync(rope.p, wide.data(), 2 * rn * 8, cudaMemcpyHostToDevice, c->stream));
-        CMFC_CUDA(cudaStreamSynchronize(c->stream));  // `wide` is a local
+        CMFC_CUDA(cudaMemcpyAsync(rope.p, a->rope_cos, rn * 4, cudaMemcpyHostToDevice, c->stream));
+        CMFC_CUDA(cudaMemcpyAsync(rope.as<float>() + rn, a->rope_sin, rn * 4, cudaMemcpyHostToDevice, c->stream));
+        CMFC_CUDA(cudaStreamSynchronize(c->stream));  // the caller's buffers are borrowed for this call only
         rope_cache.assign(a->rope_cos, a->rope_cos + rn);
         rope_cache.insert(rope_cache.end(), a->rope_sin, a->rope_sin + rn);
     }
@@ -304,7 +303,7 @@ extern "C" int cmfc_dit_block_seg(cmfc_model* m, const cmfc_dit_block_args* a, c
         return fail(ERR_BAD_ARG, "dit_block_seg: resident_in set but no state of this size is on the device");
     }
     CMFC_TRY(dev_block(c, bw, mod, c->resident_x.as<float>(), (int)n, sv, (int)hs, (int)a->inter, (int)a->nh, (int)a->nkv, (int)a->hd,
-                       (double)a->eps, rope.as<double>(), rope.as<double>() + rn));
+                       (double)a->eps, rope.as<float>(), rope.as<float>() + rn));
     if (!a->resident_out) {
         NEED(x, "dit_block_seg: x is null but resident_out is not set");
         CMFC_CUDA(cudaMemcpyAsync(x, c->resident_x.p, n * hs * 4, cudaMemcpyDeviceToHost, c->stream));
@@ -472,8 +471,9 @@ int load_block(Context* c, cmfc_nextdit* d, const std::string& p, bool modulated
     return OK;
 }
 
-// host f64 RoPE table (crates/cortiq-engine/src/dit.rs:366-381) for a list of position ids
-void rope_rows(const std::vector<int>& ids3, const int axes[3], std::vector<double>* cs, std::vector<double>* sn) {
+// host RoPE table (crates/cortiq-engine/src/dit.rs:366-381) for a list of position ids: angles, cos
+// and sin in f64, rounded once to the f32 the device kernel reads
+void rope_rows(const std::vector<int>& ids3, const int axes[3], std::vector<float>* cs, std::vector<float>* sn) {
     const size_t n = ids3.size() / 3;
     const int pairs = (axes[0] + axes[1] + axes[2]) / 2;
     cs->resize(n * pairs);
@@ -488,19 +488,19 @@ void rope_rows(const std::vector<int>& ids3, const int axes[3], std::vector<doub
     for (size_t i = 0; i < n; ++i)
         for (int j = 0; j < pairs; ++j) {
             const double ang = (double)ids3[3 * i + axis_of[j]] * freq[j];
-            (*cs)[i * pairs + j] = cos(ang);
-            (*sn)[i * pairs + j] = sin(ang);
+            (*cs)[i * pairs + j] = (float)cos(ang);
+            (*sn)[i * pairs + j] = (float)sin(ang);
         }
 }
 int upload_rope(Context* c, DevBuf* buf, const std::vector<int>& ids3, const int axes[3]) {
-    std::vector<double> cs, sn;
+    std::vector<float> cs, sn;
     rope_rows(ids3, axes, &cs, &sn);
     // kernels already queued on the stream may still read the previous table
     CMFC_CUDA(cudaStreamSynchronize(c->stream));
-    CMFC_TRY(buf->ensure(cs.size() * 16));
+    CMFC_TRY(buf->ensure(cs.size() * 8));
     // on the stream the readers run on (it is not ordered after the legacy default stream)
-    CMFC_CUDA(cudaMemcpyAsync(buf->p, cs.data(), cs.size() * 8, cudaMemcpyHostToDevice, c->stream));
-    CMFC_CUDA(cudaMemcpyAsync(buf->as<double>() + cs.size(), sn.data(), sn.size() * 8, cudaMemcpyHostToDevice, c->stream));
+    CMFC_CUDA(cudaMemcpyAsync(buf->p, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice, c->stream));
+    CMFC_CUDA(cudaMemcpyAsync(buf->as<float>() + cs.size(), sn.data(), sn.size() * 4, cudaMemcpyHostToDevice, c->stream));
     CMFC_CUDA(cudaStreamSynchronize(c->stream));  // cs / sn are locals
     return OK;
 }
@@ -522,8 +522,8 @@ int run_block(Context* c, cmfc_nextdit* d, const DitBlock& b, float* x, int n, c
         ch.next_norm1 = next->bw.norm1;
         ch.next_s_msa = next->modulated ? next_mods : nullptr;
     }
-    return dev_block(c, b.bw, mod, x, n, segs, d->hidden, d->inter, d->nh, d->nkv, d->hd, d->eps, rope.as<double>(),
-                     rope.as<double>() + half, &ch);
+    return dev_block(c, b.bw, mod, x, n, segs, d->hidden, d->inter, d->nh, d->nkv, d->hd, d->eps, rope.as<float>(),
+                     rope.as<float>() + half, &ch);
 }
 
 // y = W x + b for a small dense or q8 weight
@@ -656,7 +656,15 @@ int forward_device(Context* c, cmfc_nextdit* d, const float* latents, int batch,
         CMFC_TRY(upload_rope(c, &rope_joint, ids_joint, d->axes));
         d->rope_key[rs] = key.str();
     }
+    // Every prompt of the batch has the same token count, so the GEMMs see a stack of equal periods
+    // and may plan their K split per prompt (a prompt's result must not depend on its batch).
+    struct PeriodGuard {
+        Context* c;
+        PeriodGuard(Context* c_, int tokens) : c(c_) { c->gemm_period_tokens = tokens; }
+        ~PeriodGuard() { c->gemm_period_tokens = 0; }
+    };
     size_t mk = 0;
+    PeriodGuard img_period(c, n_img);
     for (size_t l = 0; l < d->noise_ref.size(); ++l, ++mk) {
         const DitBlock* nx = l + 1 < d->noise_ref.size() ? &d->noise_ref[l + 1] : nullptr;
         CMFC_TRY(run_block(c, d, d->noise_ref[l], img.as<float>(), batch * n_img, segs_img, mods + mk * 4 * hs, rope_img,
@@ -676,6 +684,7 @@ int forward_device(Context* c, cmfc_nextdit* d, const float* latents, int batch,
                 row += n_img;
             }
     }
+    PeriodGuard joint_period(c, n_joint / batch);
     for (size_t l = 0; l < d->layers.size(); ++l) {
         const DitBlock* nx = l + 1 < d->layers.size() ? &d->layers[l + 1] : nullptr;
         CMFC_TRY(run_block(c, d, d->layers[l], xb.as<float>(), n_joint, segs_joint, mods + mk * 4 * hs, rope_joint, (size_t)n_joint,
@@ -1131,12 +1140,12 @@ extern "C" int cmfc_bench_attention(size_t nh, size_t nkv, size_t hd, size_t n, 
 }
 
 // kind: 0 modulated RMSNorm (f32 -> bf16), 1 gated residual, 2 gated residual fused with the next
-// modulated norm, 3 qk-norm + RoPE + head packing (cols = hidden; nh/nkv/hd as Lumina-2 when hidden = 2304)
+// modulated norm, 3 qk-norm + RoPE + head packing of Q and K (cols = hidden; nh/nkv/hd as Lumina-2 when hidden = 2304)
 extern "C" int cmfc_bench_rowop(int kind, size_t rows, size_t cols, int iters, float* ms_per_launch, double* bytes_per_launch) {
     NEED(ms_per_launch && bytes_per_launch && rows && cols && iters > 0 && kind >= 0 && kind <= 3, "bench_rowop: bad argument");
     NEED_CTX();
     if (!row_cols_supported((int)cols)) return fail(ERR_UNSUPPORTED, "bench_rowop: unsupported row width");
-    DevBuf &x = c->buf("br_x"), &src = c->buf("br_src"), &vec = c->buf("br_vec"), &ob = c->buf("br_ob"), &tab = c->buf("br_tab"), &o2 = c->buf("br_o2"), &o3 = c->buf("br_o3");
+    DevBuf &x = c->buf("br_x"), &src = c->buf("br_src"), &vec = c->buf("br_vec"), &ob = c->buf("br_ob"), &tab = c->buf("br_tab"), &o2 = c->buf("br_o2");
     const int hd = cols % 96 == 0 ? 96 : 64, nh = (int)cols / hd, nkv = nh % 3 == 0 ? nh / 3 : nh;
     const size_t qkvw = (size_t)(nh + 2 * nkv) * hd;
     CMFC_TRY(x.ensure(rows * (kind == 3 ? qkvw : cols) * 4));
@@ -1147,21 +1156,17 @@ extern "C" int cmfc_bench_rowop(int kind, size_t rows, size_t cols, int iters, f
     launch_fill_normal(src.as<float>(), rows * cols, 22, 1.0f, c->stream);
     launch_fill_normal(vec.as<float>(), 4 * cols, 23, 0.1f, c->stream);
     const float* v0 = vec.as<float>();
-    std::vector<int> segs(1, (int)rows);
-    SegTable st;
     if (kind == 3) {
-        CMFC_TRY(prepare_segs(c, segs, &st));
-        CMFC_TRY(tab.ensure(rows * hd * 8));
+        CMFC_TRY(tab.ensure(rows * hd * 4));
         CMFC_TRY(o2.ensure(rows * nkv * hd * 2));
-        CMFC_TRY(o3.ensure((size_t)nkv * hd * st.vt_pitch * 2));
-        CMFC_CUDA(cudaMemsetAsync(tab.p, 0, rows * hd * 8, c->stream));
+        CMFC_CUDA(cudaMemsetAsync(tab.p, 0, rows * hd * 4, c->stream));
     }
     auto run = [&]() {
         if (kind == 0) launch_rms_mod(x.as<float>(), v0, v0 + cols, 1e-5, (int)rows, (int)cols, ob.as<__nv_bfloat16>(), nullptr, c->stream);
         else if (kind == 1) launch_gated_residual(x.as<float>(), src.as<float>(), v0, v0 + cols, 1e-5, (int)rows, (int)cols, c->stream);
         else if (kind == 2) launch_residual_then_norm(x.as<float>(), src.as<float>(), v0, v0 + cols, v0 + 2 * cols, v0 + 3 * cols, 1e-5, (int)rows, (int)cols, ob.as<__nv_bfloat16>(), c->stream);
-        else launch_qk_rope_pack(x.as<float>(), (int)rows, nh, nkv, hd, v0, v0 + hd, tab.as<double>(), tab.as<double>() + rows * hd / 2, ob.as<__nv_bfloat16>(), o2.as<__nv_bfloat16>(), o3.as<__nv_bfloat16>(), st.vt_pitch, st.dev, 1, st.max_seg, c->stream);
-        c->launches += kind == 3 ? 2 : 1;
+        else launch_qk_rope_pack(x.as<float>(), (int)rows, nh, nkv, hd, v0, v0 + hd, tab.as<float>(), tab.as<float>() + rows * hd / 2, ob.as<__nv_bfloat16>(), o2.as<__nv_bfloat16>(), c->stream);
+        c->launches++;
     };
     for (int i = 0; i < 3; ++i) run();
     cudaEvent_t e0, e1;
@@ -1178,8 +1183,10 @@ extern "C" int cmfc_bench_rowop(int kind, size_t rows, size_t cols, int iters, f
     *ms_per_launch = ms / iters;
     const double e = (double)rows * cols;
     // algorithmic bytes: f32 reads/writes 4 B, bf16 writes 2 B per element
+    // kind 3: the Q and K columns of the QKV matrix in (f32), Q and K out (bf16), the f32 cos / sin row
+    const double qkw = (double)(nh + nkv) * hd;
     *bytes_per_launch = kind == 0 ? e * 6 : kind == 1 ? e * 12 : kind == 2 ? e * 14
-                                  : (double)rows * (qkvw * 4 + qkvw * 2 + (double)(hd / 2) * 16);
+                                  : (double)rows * (qkw * 4 + qkw * 2 + (double)(hd / 2) * 8);
     CMFC_CUDA(cudaGetLastError());
     return OK;
 }

@@ -251,7 +251,9 @@ gemm_dequant_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
             auto emit = [&](const uint32_t (&v)[32], int c) {
                 const int mb = m0 + c * 32;
                 if (mb >= p.M) return;
-                if (p.mode == GEMM_OUT_F32) {
+                if (p.mode == GEMM_OUT_F32 && p.vt && n >= p.vt_row0) {
+                    emit_vt_chunk(v, rs, mb, p.M, p.vt + (size_t)(n - p.vt_row0) * p.vt_pitch, p.seg_table, p.nseg);
+                } else if (p.mode == GEMM_OUT_F32) {
                     float* out = reinterpret_cast<float*>(p.out) + (size_t)mb * p.ldo + n;
 #pragma unroll
                     for (int j = 0; j < 32; ++j)

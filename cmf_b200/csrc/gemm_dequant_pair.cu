@@ -99,29 +99,48 @@ __device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
         : "memory");
 }
 
-// Work of one CTA pair: whole tiles pair, pair + pairs, ... and, when the launch cuts the tiles of its
-// last partial wave along K (splits > 1), at most a few K slices of those tiles.
+// How a launch's tiles become work units of the CTA pairs.  Tiles are numbered token-tile major
+// (tile = token_tile * tiles_n + row_tile).  Without a K split every tile is one unit, dealt round
+// robin.  With one, the launch is a whole number of PERIODS of `period` tiles each (the tiles of one
+// prompt; the batch is a stack of equal prompts): the first `whole` tiles of every period are whole
+// units (whole is a multiple of the number of pairs, so they fill complete waves) and each of the
+// remaining period - whole tiles of every period is cut along K into `splits` slices whose partial
+// sums a second kernel adds in slice order.  Which tiles are cut, and where, depends only on the
+// position of a tile inside its prompt and on (N, K): a prompt's bits do not depend on its batch.
+struct SplitPlan {
+    int splits;   // 1: no K split
+    int period;   // tiles per period
+    int whole;    // whole-tile units per period
+    int periods;  // periods in the launch
+};
 struct Unit {
     int tile, kb0, kb1;
     int slot;  // < 0: whole tile, the epilogue writes the output; else the partial-sum slot
 };
-__device__ __forceinline__ bool unit_at(int i, int pair, int pairs, int tiles, int kblocks, int splits, Unit& u) {
-    const int waves = splits > 1 ? tiles / pairs : (tiles + pairs - 1) / pairs;
-    if (i < waves) {
+__device__ __forceinline__ bool unit_at(int i, int pair, int pairs, int tiles, int kblocks, const SplitPlan& sp, Unit& u) {
+    if (sp.splits <= 1) {
         u.tile = pair + i * pairs;
         u.kb0 = 0;
         u.kb1 = kblocks;
         u.slot = -1;
         return u.tile < tiles;
     }
-    if (splits <= 1) return false;
-    const int rem = tiles - waves * pairs;
-    const int q = pair + (i - waves) * pairs;
-    if (q >= rem * splits) return false;
-    const int sl = q % splits;
-    u.tile = waves * pairs + q / splits;
-    u.kb0 = (int)((long)sl * kblocks / splits);
-    u.kb1 = (int)((long)(sl + 1) * kblocks / splits);
+    const int n_whole = sp.periods * sp.whole;
+    const int g = pair + i * pairs;
+    if (g < n_whole) {
+        u.tile = (g / sp.whole) * sp.period + g % sp.whole;
+        u.kb0 = 0;
+        u.kb1 = kblocks;
+        u.slot = -1;
+        return true;
+    }
+    const int rem = sp.period - sp.whole;
+    const int q = g - n_whole;  // n_whole is a multiple of pairs: slices start on a fresh wave
+    if (q >= sp.periods * rem * sp.splits) return false;
+    const int sl = q % sp.splits, r = q / sp.splits;
+    u.tile = (r / rem) * sp.period + sp.whole + r % rem;
+    u.kb0 = (int)((long)sl * kblocks / sp.splits);
+    u.kb1 = (int)((long)(sl + 1) * kblocks / sp.splits);
     u.slot = q;
     return true;
 }
@@ -129,7 +148,7 @@ __device__ __forceinline__ bool unit_at(int i, int pair, int pairs, int tiles, i
 template <int WKIND>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_dequant_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
-                         const __grid_constant__ CUtensorMap tm_s, GemmParams p, int splits) {
+                         const __grid_constant__ CUtensorMap tm_s, GemmParams p, SplitPlan sp) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* x_smem = smem;
@@ -183,7 +202,7 @@ gemm_dequant_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
         if (elect_one()) {
             uint32_t it = 0;
             Unit u;
-            for (int ui = 0; unit_at(ui, pair, pairs, tiles, kblocks, splits, u) && !*abort_flag; ++ui) {
+            for (int ui = 0; unit_at(ui, pair, pairs, tiles, kblocks, sp, u) && !*abort_flag; ++ui) {
                 const int tile = u.tile;
                 const int n0 = (tile % tiles_n) * (2 * TW) + rank * TW, m0 = (tile / tiles_n) * TT + rank * TH;
                 for (int kb = u.kb0; kb < u.kb1; ++kb, ++it) {
@@ -209,7 +228,7 @@ gemm_dequant_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
             constexpr uint32_t IDESC = idesc_bf16_f32(2 * TW, TT);
             uint32_t it = 0, tile_i = 0;
             Unit u;
-            for (int ui = 0; unit_at(ui, pair, pairs, tiles, kblocks, splits, u) && !*abort_flag; ++ui, ++tile_i) {
+            for (int ui = 0; unit_at(ui, pair, pairs, tiles, kblocks, sp, u) && !*abort_flag; ++ui, ++tile_i) {
                 if (!mbar_wait(&bars->acc_empty, (tile_i & 1u) ^ 1u, abort_flag, 2)) break;
                 tc_fence_after();
                 bool ok = true;
@@ -250,7 +269,7 @@ gemm_dequant_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
             }
         };
         Unit u;
-        for (int ui = 0; unit_at(ui, pair, pairs, tiles, kblocks, splits, u) && ok && !*abort_flag; ++ui) {
+        for (int ui = 0; unit_at(ui, pair, pairs, tiles, kblocks, sp, u) && ok && !*abort_flag; ++ui) {
             for (int kb = u.kb0; kb < u.kb1; ++kb, ++it) {
                 if ((int)(it % DQ_GROUPS) != grp) continue;
                 const int s = it % STAGES, ai = it % ASTAGES;
@@ -304,7 +323,7 @@ gemm_dequant_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         uint32_t tile_i = 0;
         Unit u;
-        for (int ui = 0; unit_at(ui, pair, pairs, tiles, kblocks, splits, u) && !*abort_flag; ++ui, ++tile_i) {
+        for (int ui = 0; unit_at(ui, pair, pairs, tiles, kblocks, sp, u) && !*abort_flag; ++ui, ++tile_i) {
             const int tile = u.tile;
             const int n0 = (tile % tiles_n) * (2 * TW) + rank * TW, m0 = (tile / tiles_n) * TT;
             if (!mbar_wait<80>(&bars->acc_full, tile_i & 1u, abort_flag, 6)) break;
@@ -321,6 +340,8 @@ gemm_dequant_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
                         if (mb + j < p.M) out[(size_t)j * (2 * TW)] = __uint_as_float(v[j]) * rs;
+                } else if (p.mode == GEMM_OUT_F32 && p.vt && n >= p.vt_row0) {
+                    emit_vt_chunk(v, rs, mb, p.M, p.vt + (size_t)(n - p.vt_row0) * p.vt_pitch, p.seg_table, p.nseg);
                 } else if (p.mode == GEMM_OUT_F32) {
                     float* out = reinterpret_cast<float*>(p.out) + (size_t)mb * p.ldo + n;
 #pragma unroll
@@ -378,11 +399,11 @@ gemm_dequant_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
 }
 
 // Adds the K slices of every split tile in slice order and writes the f32 output.
-// grid (split tiles, 16): a block covers 16 of the tile's 256 tokens.
+// grid (split tiles of the launch, 16): a block covers 16 of the tile's 256 tokens.
 __global__ void __launch_bounds__(256)
-gemm_splitk_reduce_kernel(const float* __restrict__ ws, int splits, int first_tile, int tiles_n, int M, float* __restrict__ out,
-                          int ldo) {
-    const int r = blockIdx.x, tile = first_tile + r;
+gemm_splitk_reduce_kernel(const float* __restrict__ ws, SplitPlan sp, int tiles_n, int M, float* __restrict__ out, int ldo) {
+    const int r = blockIdx.x, rem = sp.period - sp.whole, splits = sp.splits;
+    const int tile = (r / rem) * sp.period + sp.whole + r % rem;
     const int n0 = (tile % tiles_n) * (2 * TW), m0 = (tile / tiles_n) * TT;
     const int col = (threadIdx.x & 63) * 4;
 #pragma unroll
@@ -402,6 +423,38 @@ gemm_splitk_reduce_kernel(const float* __restrict__ ws, int splits, int first_ti
 
 bool gemm_pair_supported(const GemmParams& p) { return p.K % BK == 0 && p.N % (2 * TW) == 0 && p.M > 0; }
 int gemm_pair_tile_tokens() { return TH; }
+
+// The K-split plan of a launch (splits == 1: none).  `period_tokens`: tokens of one prompt when the
+// launch is a stack of equal prompts, 0 when the launch is to be treated as a single period.
+static SplitPlan plan_split(const GemmParams& p, int pairs, int period_tokens) {
+    SplitPlan sp = {1, 0, 0, 0};
+    const int tiles_n = p.N / (2 * TW), tiles_m = (p.M + TT - 1) / TT, kblocks = p.K / BK;
+    if (p.mode != GEMM_OUT_F32 || p.vt || p.ldo % 4 || (reinterpret_cast<uintptr_t>(p.out) & 15)) return sp;
+    int period_m = tiles_m, periods = 1;
+    if (period_tokens > 0) {
+        if (period_tokens % TT || p.M % period_tokens) return sp;  // prompts must start on tile boundaries
+        period_m = period_tokens / TT;
+        periods = p.M / period_tokens;
+    }
+    const int period = period_m * tiles_n, rem = period % pairs;
+    // A partial wave that fills less than half of the pairs is cut along K instead: its tiles become
+    // `splits` slices each, one slice per pair at most.  A slice shorter than 16 k-blocks is mostly ring
+    // fill and drain, and a short K gains less than the reduction launch costs (measured: K = 2304 no
+    // gain, K = 9216 +6 %).
+    if (period <= pairs || rem == 0 || 2 * rem > pairs || kblocks < 64) return sp;
+    const int splits = std::min(pairs / rem, kblocks / 16);
+    if (splits < 2) return sp;
+    sp.splits = splits; sp.period = period; sp.whole = period - rem; sp.periods = periods;
+    return sp;
+}
+
+size_t gemm_pair_splitk_bytes(const GemmParams& p, int num_sms, int period_tokens) {
+    if (!gemm_pair_supported(p)) return 0;
+    const int tiles = ((p.M + TT - 1) / TT) * (p.N / (2 * TW));
+    const int pairs = std::min(num_sms / 2, tiles);
+    const SplitPlan sp = plan_split(p, pairs, period_tokens);
+    return sp.splits > 1 ? (size_t)sp.periods * (sp.period - sp.whole) * sp.splits * GEMM_SPLITK_SLOT_BYTES : 0;
+}
 
 int launch_gemm_dequant_pair(int wkind, const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUtensorMap& tm_s,
                              const GemmParams& p, int num_sms, cudaStream_t stream) {
@@ -429,21 +482,12 @@ int launch_gemm_dequant_pair(int wkind, const CUtensorMap& tm_x, const CUtensorM
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    // A last wave that fills less than half of the pairs is cut along K instead: its tiles become
-    // `splits` slices each, spread over all pairs (one slice per pair at most).
-    int splits = 1;
-    const int kblocks = p.K / BK, rem = tiles % pairs;
-    if (p.mode == GEMM_OUT_F32 && p.splitk_ws && tiles > pairs && rem > 0 && 2 * rem <= pairs && p.ldo % 4 == 0 &&
-        (reinterpret_cast<uintptr_t>(p.out) & 15) == 0) {
-        // a slice shorter than 16 k-blocks is mostly ring fill and drain, and a short K gains less
-        // than the reduction launch costs (measured: K = 2304 no gain, K = 9216 +6 %)
-        splits = kblocks >= 64 ? std::min(pairs / rem, kblocks / 16) : 1;
-        if (splits < 2) splits = 1;
-    }
-    CMFC_CUDA(cudaLaunchKernelEx(&cfg, kern, tm_x, tm_w, tm_s, p, splits));
-    if (splits > 1) {
-        gemm_splitk_reduce_kernel<<<dim3(rem, TT / 16), 256, 0, stream>>>(p.splitk_ws, splits, tiles - rem, p.N / (2 * TW), p.M,
-                                                                        reinterpret_cast<float*>(p.out), p.ldo);
+    SplitPlan sp = {1, 0, 0, 0};
+    if (p.splitk_ws) sp = plan_split(p, pairs, p.split_period_tokens);
+    CMFC_CUDA(cudaLaunchKernelEx(&cfg, kern, tm_x, tm_w, tm_s, p, sp));
+    if (sp.splits > 1) {
+        gemm_splitk_reduce_kernel<<<dim3(sp.periods * (sp.period - sp.whole), TT / 16), 256, 0, stream>>>(
+            p.splitk_ws, sp, p.N / (2 * TW), p.M, reinterpret_cast<float*>(p.out), p.ldo);
         CMFC_CUDA(cudaGetLastError());
     }
     return OK;

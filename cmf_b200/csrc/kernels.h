@@ -19,10 +19,20 @@ struct GemmParams {
     int mode;
     const float* row_scale;  // q8 only: [N]
     uint32_t* status;        // device word; a kernel that ran out of wait budget records the site
-    // pair kernel, f32 output only: the tiles of a last, mostly empty wave are cut along K into
-    // slices that spread over all CTA pairs; the slices' partial sums land here ([slot][256 tokens][256
-    // rows] f32, at most one slot per CTA pair) and a second kernel adds them in slice order
+    // pair kernel, f32 output only: the tiles of a mostly empty last wave (of every prompt of the
+    // batch, see gemm_dequant_pair.cu) are cut along K into slices that spread over all CTA pairs; the
+    // slices' partial sums land here ([slot][256 tokens][256 rows] f32, gemm_pair_splitk_bytes() in all)
+    // and a second kernel adds them in slice order.  split_period_tokens: tokens of one prompt when the
+    // launch is a stack of equal prompts (each a multiple of 256 tokens), 0 = the launch is one period.
     float* splitk_ws = nullptr;
+    int split_period_tokens = 0;
+    // f32 output of a fused QKV projection: weight rows >= vt_row0 are V channels and are written
+    // as bf16 rows of V^T [N - vt_row0, vt_pitch] instead (token m of segment z at column
+    // seg_table[nseg + 1 + z] + m - seg_table[z]); the f32 columns of those rows are left untouched.
+    // vt == nullptr: plain output.  vt_row0 must be a multiple of 32.
+    __nv_bfloat16* vt = nullptr;
+    int vt_row0 = 0, vt_pitch = 0, nseg = 0;
+    const int* seg_table = nullptr;  // device: [nseg + 1] token offsets, then [nseg] first V^T columns
 };
 constexpr size_t GEMM_SPLITK_SLOT_BYTES = 256 * 256 * 4;
 
@@ -36,6 +46,8 @@ int launch_gemm_dequant(int wkind, const CUtensorMap& tm_x, const CUtensorMap& t
 // gemm_pair_tile_tokens() rows.
 bool gemm_pair_supported(const GemmParams& p);
 int gemm_pair_tile_tokens();
+// bytes of GemmParams::splitk_ws this launch would use (0: the launch is not split)
+size_t gemm_pair_splitk_bytes(const GemmParams& p, int num_sms, int period_tokens);
 int launch_gemm_dequant_pair(int wkind, const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUtensorMap& tm_s,
                              const GemmParams& p, int num_sms, cudaStream_t stream);
 
@@ -87,12 +99,11 @@ void launch_gated_residual(float* x, const float* src, const float* w, const flo
 void launch_residual_then_norm(float* x, const float* src, const float* w_res, const float* gate,
                                const float* w_next, const float* shift, double eps, int rows, int cols,
                                __nv_bfloat16* out_bf16, cudaStream_t s);
-// per (token, head): qk RMS norm (eps 1e-5) + interleaved-pair RoPE in f64; writes Q,K bf16
-// token-major and V^T bf16 [nkv*hd, vt_pitch]
+// per (token, head): qk RMS norm (eps 1e-5) + interleaved-pair RoPE (cos / sin [n, hd/2] f32); writes Q, K bf16
+// token-major (V never passes through here: the QKV GEMM's epilogue writes V^T itself)
 void launch_qk_rope_pack(const float* qkv, int n, int nh, int nkv, int hd, const float* norm_q,
-                         const float* norm_k, const double* cos_t, const double* sin_t, __nv_bfloat16* q,
-                         __nv_bfloat16* k, __nv_bfloat16* vt, int vt_pitch, const int* seg_table, int nseg, int max_seg,
-                         cudaStream_t s);
+                         const float* norm_k, const float* cos_t, const float* sin_t, __nv_bfloat16* q,
+                         __nv_bfloat16* k, cudaStream_t s);
 // y[r] = act_out( dot(W[r, :], act_in(x)) * scale[r] + b[r] ); W f32 or int8 (+row scales)
 // act_in: 0 none, 1 silu.  tanh_lo..tanh_hi: rows in [lo0,hi0) or [lo1,hi1) get tanh.
 struct GemvParams {

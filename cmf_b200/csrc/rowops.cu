@@ -1,9 +1,10 @@
 // Bandwidth-bound row kernels of the NextDiT block: modulated RMSNorm, gated sandwich-norm
-// residual, qk-norm + RoPE + head packing, adaLN / time-embedding matvecs, patchify,
+// residual, qk-norm + RoPE + head packing (V is packed by the QKV GEMM's epilogue), adaLN / time-embedding matvecs, patchify,
 // final LayerNorm, CFG combine + Euler step.  One warp owns one row and keeps it in
 // registers, so every tensor is read once and written once with 16-byte accesses.
-// Norm statistics and the RoPE rotation run in f64, as the reference's CPU path does
-// (crates/cortiq-engine/src/dit.rs:259-284, :1078-1102).
+// Norm statistics are accumulated in f64 (the reference's CPU path keeps them and the RoPE rotation
+// in f64, crates/cortiq-engine/src/dit.rs:259-284, :1078-1102; what runs in f32 here is stated at
+// each kernel).
 #include "common.cuh"
 #include "kernels.h"
 
@@ -21,8 +22,17 @@ __device__ __forceinline__ void st_bf16x4(__nv_bfloat16* p, float a, float b, fl
     *reinterpret_cast<uint2*>(p) = v;
 }
 
-// rms(v; w, eps) element: f32( f64(v) * inv ) * w     (dit.rs:269-275)
-__device__ __forceinline__ float rms_elem(float v, double inv, float w) { return (float)((double)v * inv) * w; }
+// Row statistics: the squares of four neighbouring values are summed in f32 (relative error
+// below 2^-22) and those partial sums are accumulated in f64 across the row and the warp; the
+// reciprocal root is taken in f64 and rounded once to f32.  The reference keeps every square and
+// the scaling product in f64 (dit.rs:269-275); the difference, about 1e-7 relative per element, is
+// far below the bf16 rounding of the GEMM operands that follows, and conversions between f32 and
+// f64 (16 per clock per SM) no longer bound these kernels.
+__device__ __forceinline__ double sq4(const float4& v) {
+    return (double)fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, v.w * v.w)));
+}
+// rms(v; w, eps) element: (v * inv) * w
+__device__ __forceinline__ float rms_elem(float v, float inv, float w) { return (v * inv) * w; }
 
 template <int NV>  // float4 per lane; cols = 128 * NV
 __global__ void __launch_bounds__(32 * ROW_WARPS)
@@ -38,10 +48,10 @@ rms_mod_kernel(const float* __restrict__ x, const float* __restrict__ w, const f
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         v[i] = ld4(xr + (i * 32 + lane) * 4);
-        ss += (double)v[i].x * v[i].x + (double)v[i].y * v[i].y + (double)v[i].z * v[i].z + (double)v[i].w * v[i].w;
+        ss += sq4(v[i]);
     }
     ss = warp_sum(ss);
-    const double inv = 1.0 / sqrt(ss / cols + eps);
+    const float inv = (float)(1.0 / sqrt(ss / cols + eps));
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         const int c = (i * 32 + lane) * 4;
@@ -80,10 +90,9 @@ residual_kernel(float* __restrict__ x, const float* __restrict__ src, const floa
     for (int i = 0; i < NV; ++i) xin[i] = ld4(xr + (i * 32 + lane) * 4);
     double ss = 0.0;
 #pragma unroll
-    for (int i = 0; i < NV; ++i)
-        ss += (double)d[i].x * d[i].x + (double)d[i].y * d[i].y + (double)d[i].z * d[i].z + (double)d[i].w * d[i].w;
+    for (int i = 0; i < NV; ++i) ss += sq4(d[i]);
     ss = warp_sum(ss);
-    const double inv = 1.0 / sqrt(ss / cols + eps);
+    const float inv = (float)(1.0 / sqrt(ss / cols + eps));
     double ss2 = 0.0;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
@@ -102,12 +111,12 @@ residual_kernel(float* __restrict__ x, const float* __restrict__ src, const floa
         st4(xr + c, xv);
         if (THEN_NORM) {
             d[i] = xv;
-            ss2 += (double)xv.x * xv.x + (double)xv.y * xv.y + (double)xv.z * xv.z + (double)xv.w * xv.w;
+            ss2 += sq4(xv);
         }
     }
     if (THEN_NORM) {
         ss2 = warp_sum(ss2);
-        const double inv2 = 1.0 / sqrt(ss2 / cols + eps);
+        const float inv2 = (float)(1.0 / sqrt(ss2 / cols + eps));
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
             const int c = (i * 32 + lane) * 4;
@@ -177,13 +186,15 @@ layernorm_scale_kernel(const float* __restrict__ x, const float* __restrict__ sc
     }
 
 // qk-norm + RoPE: four lanes own one (token, head); of every 32 consecutive elements of the head a
-// lane holds eight (four rotation pairs): two 16-byte loads, one 16-byte store, and the f64
-// square root and division of the statistic are paid once per eight heads of a warp.
+// lane holds eight (four rotation pairs): two 16-byte loads, one 16-byte store.  The head statistic
+// is accumulated in f64 (see sq4); normalisation and the rotation (a c - b s, a s + b c) run in f32
+// with cos / sin tables that the host computed in f64 and rounded once (the reference rotates in
+// f64, dit.rs:1078-1102; the results here are rounded to bf16 right after).
 constexpr int ROPE_THREADS = 128;
 template <int PPL>  // hd / 32
 __global__ void __launch_bounds__(ROPE_THREADS, PPL <= 3 ? 8 : 4)
 qk_rope_kernel(const float* __restrict__ qkv, int n, int nh, int nkv, const float* __restrict__ norm_q,
-               const float* __restrict__ norm_k, const double* __restrict__ cos_t, const double* __restrict__ sin_t,
+               const float* __restrict__ norm_k, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_out) {
     constexpr int hd = 32 * PPL;
     const int heads = nh + nkv;
@@ -196,6 +207,8 @@ qk_rope_kernel(const float* __restrict__ qkv, int n, int nh, int nkv, const floa
     const int ld_in = (nh + 2 * nkv) * hd;
     const float* src = qkv + (size_t)tok * ld_in + (size_t)h * hd + l * 8;  // q heads then k heads are contiguous
     const float* w = (is_q ? norm_q : norm_k) + l * 8;
+    const float* ct = cos_t + (size_t)tok * (hd / 2) + l * 4;
+    const float* st = sin_t + (size_t)tok * (hd / 2) + l * 4;
     float4 v[PPL][2];
 #pragma unroll
     for (int g = 0; g < PPL; ++g) {
@@ -204,70 +217,27 @@ qk_rope_kernel(const float* __restrict__ qkv, int n, int nh, int nkv, const floa
     }
     double ss = 0.0;
 #pragma unroll
-    for (int g = 0; g < PPL; ++g)
-#pragma unroll
-        for (int u = 0; u < 2; ++u)
-            ss += (double)v[g][u].x * v[g][u].x + (double)v[g][u].y * v[g][u].y + (double)v[g][u].z * v[g][u].z +
-                  (double)v[g][u].w * v[g][u].w;
+    for (int g = 0; g < PPL; ++g) ss += sq4(v[g][0]) + sq4(v[g][1]);
     ss += __shfl_xor_sync(0xffffffffu, ss, 2);
     ss += __shfl_xor_sync(0xffffffffu, ss, 1);
-    const double inv = 1.0 / sqrt(ss / hd + 1e-5);
+    const float inv = (float)(1.0 / sqrt(ss / hd + 1e-5));
     if (!active) return;
     __nv_bfloat16* dst = (is_q ? q_out + (size_t)tok * nh * hd + (size_t)h * hd
                                : k_out + (size_t)tok * nkv * hd + (size_t)(h - nh) * hd) + l * 8;
-    const double* ct = cos_t + (size_t)tok * (hd / 2) + l * 4;
-    const double* st = sin_t + (size_t)tok * (hd / 2) + l * 4;
 #pragma unroll
     for (int g = 0; g < PPL; ++g) {
         const float4 g0 = ld4(w + g * 32), g1 = ld4(w + g * 32 + 4);
-        const double2 c01 = *reinterpret_cast<const double2*>(ct + g * 16), c23 = *reinterpret_cast<const double2*>(ct + g * 16 + 2);
-        const double2 s01 = *reinterpret_cast<const double2*>(st + g * 16), s23 = *reinterpret_cast<const double2*>(st + g * 16 + 2);
-        auto rot = [&](float x, float y, float gx, float gy, double c, double s) {
-            const double a = (double)rms_elem(x, inv, gx), b = (double)rms_elem(y, inv, gy);
-            return pack_bf16((float)(a * c - b * s), (float)(a * s + b * c));
+        const float4 cs = ld4(ct + g * 16), sn = ld4(st + g * 16);
+        auto rot = [&](float x, float y, float gx, float gy, float c, float s_) {
+            const float a = rms_elem(x, inv, gx), b = rms_elem(y, inv, gy);
+            return pack_bf16(fmaf(a, c, -(b * s_)), fmaf(a, s_, b * c));
         };
         uint4 o;
-        o.x = rot(v[g][0].x, v[g][0].y, g0.x, g0.y, c01.x, s01.x);
-        o.y = rot(v[g][0].z, v[g][0].w, g0.z, g0.w, c01.y, s01.y);
-        o.z = rot(v[g][1].x, v[g][1].y, g1.x, g1.y, c23.x, s23.x);
-        o.w = rot(v[g][1].z, v[g][1].w, g1.z, g1.w, c23.y, s23.y);
+        o.x = rot(v[g][0].x, v[g][0].y, g0.x, g0.y, cs.x, sn.x);
+        o.y = rot(v[g][0].z, v[g][0].w, g0.z, g0.w, cs.y, sn.y);
+        o.z = rot(v[g][1].x, v[g][1].y, g1.x, g1.y, cs.z, sn.z);
+        o.w = rot(v[g][1].z, v[g][1].w, g1.z, g1.w, cs.w, sn.w);
         *reinterpret_cast<uint4*>(dst + g * 32) = o;
-    }
-}
-
-// V [n, ld_in] f32 (columns v_off + [0, width)) -> V^T bf16 [width, vt_pitch], tiles of 64 tokens x
-// 64 dims via shared memory (256-byte reads, 128-byte writes).  Segment z's tokens land at columns
-// seg_table[nseg+1+z] + local index, so each segment starts on an 8-column boundary; pad columns
-// are written as zero.
-__global__ void __launch_bounds__(256)
-v_transpose_kernel(const float* __restrict__ qkv, int ld_in, int v_off, int width, __nv_bfloat16* __restrict__ vt,
-                   int vt_pitch, const int* __restrict__ seg_table, int nseg) {
-    __shared__ float tile[64][65];
-    const int z = blockIdx.z;
-    const int seg0 = seg_table[z], len = seg_table[z + 1] - seg0, col0 = seg_table[nseg + 1 + z];
-    const int t0 = blockIdx.x * 64, d0 = blockIdx.y * 64;
-    if (t0 >= len) return;
-    const int padded = (len + 7) & ~7;
-    const int lane = threadIdx.x & 31, wp = threadIdx.x >> 5;
-    float a[8], b[8];  // sixteen loads in flight per thread
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const int tok = t0 + wp + 8 * i;
-        const float* src = qkv + (size_t)(seg0 + tok) * ld_in + v_off + d0;
-        a[i] = (tok < len && d0 + lane < width) ? src[lane] : 0.0f;
-        b[i] = (tok < len && d0 + lane + 32 < width) ? src[lane + 32] : 0.0f;
-    }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        tile[wp + 8 * i][lane] = a[i];
-        tile[wp + 8 * i][lane + 32] = b[i];
-    }
-    __syncthreads();
-#pragma unroll
-    for (int r = wp; r < 64; r += 8) {
-        const int d = d0 + r, tok = t0 + 2 * lane;  // padded is even: a token pair is inside or outside together
-        if (d < width && tok < padded)
-            *reinterpret_cast<uint32_t*>(vt + (size_t)d * vt_pitch + col0 + tok) = pack_bf16(tile[2 * lane][r], tile[2 * lane + 1][r]);
     }
 }
 
@@ -526,9 +496,8 @@ bool row_cols_supported(int cols) {
 }
 
 void launch_qk_rope_pack(const float* qkv, int n, int nh, int nkv, int hd, const float* norm_q,
-                         const float* norm_k, const double* cos_t, const double* sin_t, __nv_bfloat16* q,
-                         __nv_bfloat16* k, __nv_bfloat16* vt, int vt_pitch, const int* seg_table, int nseg, int max_seg,
-                         cudaStream_t s) {
+                         const float* norm_k, const float* cos_t, const float* sin_t, __nv_bfloat16* q,
+                         __nv_bfloat16* k, cudaStream_t s) {
     const long items = (long)n * (nh + nkv);
     const int grid = (int)((items + ROPE_THREADS / 4 - 1) / (ROPE_THREADS / 4));
     switch (hd / 32) {
@@ -538,9 +507,6 @@ void launch_qk_rope_pack(const float* qkv, int n, int nh, int nkv, int hd, const
         case 4: qk_rope_kernel<4><<<grid, ROPE_THREADS, 0, s>>>(qkv, n, nh, nkv, norm_q, norm_k, cos_t, sin_t, q, k); break;
         default: break;
     }
-    const int ld_in = (nh + 2 * nkv) * hd, width = nkv * hd;
-    dim3 g((max_seg + 63) / 64, (width + 63) / 64, nseg);
-    v_transpose_kernel<<<g, 256, 0, s>>>(qkv, ld_in, (nh + nkv) * hd, width, vt, vt_pitch, seg_table, nseg);
 }
 void launch_interleave_f32(float* dst, int dst_stride, int dst_off, const float* src, size_t count, cudaStream_t s) {
     interleave_f32_kernel<<<grid_for(count, 256), 256, 0, s>>>(dst, dst_stride, dst_off, src, count);

@@ -160,7 +160,6 @@ int ctx_set_device(int device) {
             l2[h] = log2f(f);
             e2[h] = exp2f(f);
         }
-        CMFC_CUDA(cudaMalloc(&c->splitk_ws, (size_t)(c->num_sms / 2) * GEMM_SPLITK_SLOT_BYTES));
         CMFC_CUDA(cudaMalloc(&c->log2_lut, 65536 * 4));
         CMFC_CUDA(cudaMalloc(&c->exp2_lut, 65536 * 4));
         CMFC_CUDA(cudaMemcpy(c->log2_lut, l2.data(), 65536 * 4, cudaMemcpyHostToDevice));
@@ -584,7 +583,7 @@ int get_weight_interleaved(Context* c, Model* m, int64_t a, int64_t b, DevWeight
 }
 
 // ---------------- device-level ops ----------------
-int dev_gemm(Context* c, DevWeight* w, const __nv_bfloat16* x, int M, void* out, int ldo, int mode) {
+int dev_gemm(Context* c, DevWeight* w, const __nv_bfloat16* x, int M, void* out, int ldo, int mode, const GemmVt* vt) {
     if (!w->gemm_ready)
         return fail(ERR_SHAPE, "dequant GEMM needs rows % 128 == 0 and cols % 64 == 0 (got " + std::to_string(w->rows) +
                                    " x " + std::to_string(w->cols) + ")");
@@ -593,11 +592,10 @@ int dev_gemm(Context* c, DevWeight* w, const __nv_bfloat16* x, int M, void* out,
     p.out = out; p.ldo = ldo; p.mode = mode;
     p.row_scale = w->dtype == DT_Q8 ? w->scales : nullptr;
     p.status = c->status;
-    // Cutting a last partial wave along K is opt-in (CMFC_GEMM_SPLITK=1): which tiles are cut depends
-    // on the token count, so with it on a prompt's result depends (in the last f32 bits of a GEMM,
-    // then through bf16 rounding flips) on what else is in its batch.
-    const char* split_env = getenv("CMFC_GEMM_SPLITK");
-    p.splitk_ws = (split_env && split_env[0] == '1') ? c->splitk_ws : nullptr;
+    if (vt) {
+        if (mode != GEMM_OUT_F32 || vt->row0 % 32 || vt->row0 > w->rows) return fail(ERR_BAD_ARG, "dev_gemm: bad V^T split");
+        p.vt = vt->vt; p.vt_row0 = vt->row0; p.vt_pitch = vt->pitch; p.nseg = vt->nseg; p.seg_table = vt->seg_table;
+    }
     const int wkind = w->dtype == DT_Q8 ? 0 : (w->dtype == DT_Q4TP ? 1 : 2);
     // CTA-pair kernel (2-SM MMA) whenever the weight rows tile by 256 and there is at least one
     // tile per pair of SMs; otherwise the single-CTA kernel.  CMFC_GEMM_PAIR=0 forces the latter.
@@ -605,6 +603,29 @@ int dev_gemm(Context* c, DevWeight* w, const __nv_bfloat16* x, int M, void* out,
     const bool use_pair = !(pair_env && pair_env[0] == '0');
     const long pair_tiles = (long)((M + 255) / 256) * (w->rows / 256);
     const bool pair = use_pair && gemm_pair_supported(p) && pair_tiles >= c->num_sms / 2;
+    // K split of a mostly empty last wave (pair kernel, f32 output).  Inside a NextDiT forward the
+    // batch is a stack of equal prompts and the split is planned per prompt (c->gemm_period_tokens),
+    // so a prompt's bits do not depend on its batch.  A launch without that structure is split only
+    // on request: CMFC_GEMM_SPLITK=1 treats the whole launch as one period (its result then depends
+    // on the token count in the last f32 bits), a value of 256 or more is the period in tokens.
+    // CMFC_GEMM_SPLITK=0 turns the split off everywhere.
+    if (pair && mode == GEMM_OUT_F32 && !vt) {
+        const char* split_env = getenv("CMFC_GEMM_SPLITK");  // read per call: tests flip it between calls
+        const int asked = split_env ? atoi(split_env) : -1;
+        const bool off = asked == 0, force = asked == 1;
+        int period = c->gemm_period_tokens > 0 && M % c->gemm_period_tokens == 0 ? c->gemm_period_tokens : 0;
+        if (!period && asked >= 256 && M % asked == 0) period = asked;
+        if (!off && (period > 0 || force)) {
+            const size_t need = gemm_pair_splitk_bytes(p, c->num_sms, period);
+            if (need) {
+                DevBuf& ws = c->buf("gemm_splitk");
+                CMFC_TRY(ws.ensure(need));
+                p.splitk_ws = ws.as<float>();
+                p.split_period_tokens = period;
+                c->launches++;  // the kernel that adds the slices
+            }
+        }
+    }
     CUtensorMap tm_x;
     CMFC_TRY(make_tensor_map_2d(&tm_x, x, 2, (uint64_t)M, (uint64_t)w->cols, (uint64_t)w->cols * 2,
                                 pair ? gemm_pair_tile_tokens() : gemm_tile_tokens(), 64, 3));
@@ -666,7 +687,7 @@ int dev_attention(Context* c, const __nv_bfloat16* q, const __nv_bfloat16* k, co
 }
 
 int dev_block(Context* c, const BlockWeights& bw, const BlockMod& mod, float* x, int n, const std::vector<int>& segs,
-              int hidden, int inter, int nh, int nkv, int hd, double eps, const double* cos_t, const double* sin_t,
+              int hidden, int inter, int nh, int nkv, int hd, double eps, const float* cos_t, const float* sin_t,
               const BlockChain* chain) {
     cudaStream_t s = c->stream;
     const int qkv_w = (nh + 2 * nkv) * hd;
@@ -694,14 +715,16 @@ int dev_block(Context* c, const BlockWeights& bw, const BlockMod& mod, float* x,
         c->launches++;
     }
     {
+        // Q and K leave the GEMM as f32 (the head norm comes first); V goes straight to V^T in bf16
         SpanGuard g(c, "qkv-proj");
-        CMFC_TRY(dev_gemm(c, bw.qkv, xn.as<__nv_bfloat16>(), n, qkv.p, qkv_w, GEMM_OUT_F32));
+        const GemmVt gv = {vt.as<__nv_bfloat16>(), (nh + nkv) * hd, vt_pitch, (int)segs.size(), st.dev};
+        CMFC_TRY(dev_gemm(c, bw.qkv, xn.as<__nv_bfloat16>(), n, qkv.p, qkv_w, GEMM_OUT_F32, &gv));
     }
     {
         SpanGuard g(c, "rope");
         launch_qk_rope_pack(qkv.as<float>(), n, nh, nkv, hd, bw.norm_q, bw.norm_k, cos_t, sin_t, qb.as<__nv_bfloat16>(),
-                            kb.as<__nv_bfloat16>(), vt.as<__nv_bfloat16>(), vt_pitch, st.dev, (int)segs.size(), st.max_seg, s);
-        c->launches += 2;
+                            kb.as<__nv_bfloat16>(), s);
+        c->launches++;
     }
     {
         SpanGuard g(c, "attention");

@@ -96,7 +96,7 @@ struct Context {
     std::vector<float> facade_rope_host;  // the caller's f32 RoPE table that ws["facade_rope"] currently holds
     DevBuf resident_x;                 // hidden state kept between chained dit_block_seg calls
     size_t resident_len = 0;
-    float* splitk_ws = nullptr;        // partial sums of the pair GEMM's K slices: one slot per CTA pair
+    int gemm_period_tokens = 0;        // tokens per prompt while a forward runs a stack of equal prompts (else 0)
     float* log2_lut = nullptr;         // [65536] log2f of every f16 value (host libm)
     float* exp2_lut = nullptr;         // [65536] exp2f of every f16 value
     uint64_t launches = 0;
@@ -118,7 +118,14 @@ int get_weight_interleaved(Context* c, Model* m, int64_t a, int64_t b, DevWeight
 int upload_f32(Context* c, Model* m, int64_t idx, DevWeight** out);  // any float tensor -> dense f32
 
 // device-level ops (device pointers; async on c->stream)
-int dev_gemm(Context* c, DevWeight* w, const __nv_bfloat16* x, int M, void* out, int ldo, int mode);
+// V^T destination of a fused QKV projection (see GemmParams::vt)
+struct GemmVt {
+    __nv_bfloat16* vt;
+    int row0, pitch, nseg;
+    const int* seg_table;
+};
+int dev_gemm(Context* c, DevWeight* w, const __nv_bfloat16* x, int M, void* out, int ldo, int mode,
+             const GemmVt* vt = nullptr);
 int prepare_segs(Context* c, const std::vector<int>& segs, SegTable* out);
 int dev_attention(Context* c, const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* vt,
                   const SegTable& st, int nh, int nkv, int hd, float scale, __nv_bfloat16* out);
@@ -141,7 +148,7 @@ struct BlockChain {
     const float* next_s_msa = nullptr;  // next block's s_msa (null for an unmodulated block)
 };
 int dev_block(Context* c, const BlockWeights& bw, const BlockMod& mod, float* x, int n, const std::vector<int>& segs,
-              int hidden, int inter, int nh, int nkv, int hd, double eps, const double* cos_t, const double* sin_t,
+              int hidden, int inter, int nh, int nkv, int hd, double eps, const float* cos_t, const float* sin_t,
               const BlockChain* chain = nullptr);
 
 bool row_cols_supported(int cols);

@@ -98,7 +98,8 @@ def test_block_seg_rejects_bad_segments(tmp_path):
 
 @pytest.mark.parametrize("plan_name", ["q8", "q4tp_ffn_q8_attn", "q4t"])
 def test_tiny_forward_pair_per_block_and_latent(tmp_path, plan_name):
-    """BASELINE config 1 (tiny, batch 1, t = 0.5, seed 0) plus the mixed-codec variants."""
+    """The tiny CPU-runnable denoiser (2 layers, hidden 256, q8 per-row weights, 32x32 latent, 32 caption
+    tokens, batch 1, t = 0.5, seed 0) plus the mixed-codec variants."""
     from cmf_b200 import Model, NextDit
     cfg = synth.TINY
     attn, ffn = {"q8": (oc.Q8_ROW, oc.Q8_ROW), "q4tp_ffn_q8_attn": (oc.Q8_ROW, oc.Q4TP),

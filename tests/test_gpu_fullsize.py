@@ -1,7 +1,7 @@
-"""Full-size cases of the baseline configs, checked through size-independent properties (the CPU
-oracle cannot run them in seconds): linearity and row-sampled parity of the largest sweep GEMM,
-and for the 2.6 B model at 1024x1024 the equality of the batched CFG pair with two single
-forwards and of a batch with its prompts run alone."""
+"""Full-size cases (the largest sweep GEMM, the 2.6 B model at 1024x1024) checked through
+size-independent properties, since the CPU oracle cannot run them in seconds: linearity and
+row-sampled parity of the largest sweep GEMM; equality of the batched CFG pair with two single
+forwards, and of a batch with its prompts run alone."""
 import os
 
 import numpy as np
@@ -41,8 +41,8 @@ def test_sweep_gemm_largest_shape_linearity_and_samples(tmp_path, codec):
     assert rel_l2(y1[pick], want) < (2e-5 if codec == "q8" else 4e-3)
 
 
-def test_lumina_1024_pair_single_and_batch_consistency(tmp_path):
-    """Config-4 codec mix (q4tp FFN + q8 attention) at 1024x1024, 256 caption tokens."""
+def test_lumina_1024_pair_single_and_batch_consistency(tmp_path, monkeypatch):
+    """The 2.6 B model with q4tp feed-forward and q8 attention weights at 1024x1024, 256 caption tokens."""
     from cmf_b200 import GenParams, Model, NextDit, denoise, synth
     path = os.path.join(str(tmp_path), "lumina.cmf")
     synth.write_model(path, synth.LUMINA2, attn="q8", ffn="q4tp", seed=0)
@@ -65,4 +65,19 @@ def test_lumina_1024_pair_single_and_batch_consistency(tmp_path):
         both = denoise(dit, lat, cap, cap_u, p)
         one = denoise(dit, lat[1:2], cap[1:2], cap_u[1:2], p)
         assert rel_l2(one[0], both[1]) < 1e-5                # a prompt's result does not depend on its batch
+        # The feed-forward down projection (K = 9216; 306 tiles per prompt on 74 CTA pairs) runs with
+        # the last 10 tiles of EVERY prompt cut along K; the plan depends on the position inside the
+        # prompt only, which is what keeps the line above true.  Without the split: one launch less
+        # per joint block (the kernel that adds the slices), the same result up to f32 summation order.
+        from cmf_b200 import gpu
+        gpu.launch_count(reset=True)
+        pc2, _ = dit.forward_cfg_pair(lat[0], 128, 128, cc, 256, cu, 256, 0.5)
+        with_split = gpu.launch_count(reset=True)
+        monkeypatch.setenv("CMFC_GEMM_SPLITK", "0")
+        pc3, _ = dit.forward_cfg_pair(lat[0], 128, 128, cc, 256, cu, 256, 0.5)
+        without = gpu.launch_count(reset=True)
+        monkeypatch.delenv("CMFC_GEMM_SPLITK")
+        assert np.array_equal(pc, pc2)
+        assert with_split - without == 26, (with_split, without)
+        assert rel_l2(pc2, pc3) < 2e-3, rel_l2(pc2, pc3)
         dit.close()

@@ -225,3 +225,37 @@ def test_pair_kernel_k_split_of_last_wave(tmp_path, monkeypatch, dt, M, K, N):
         else:
             differs += not same
     assert differs > 0      # the split path really ran
+
+
+@pytest.mark.parametrize("dt", [oc.Q4_TILED, oc.Q4TP])
+def test_k_split_planned_per_prompt_is_batch_independent(tmp_path, monkeypatch, dt):
+    """Inside a forward the K split is planned per prompt (period): the last 10 of the 306 tiles of
+    EVERY 8704-token prompt are cut, whatever the number of prompts in the launch.  A stack of two
+    prompts therefore gives each prompt the bits it gets alone, while the split tiles differ from the
+    unsplit kernel in the f32 summation order only."""
+    from cmf_b200 import Model, gpu
+    K, N, T = 9216, 2304, 8704
+    rng = np.random.default_rng(11)
+    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    x = oc.bf16_round(rng.standard_normal((2 * T, K)).astype(np.float32))
+    path = str(tmp_path / "w.cmf")
+    single_weight_file(path, [("w", dt, w)])
+    with Model(path) as m:
+        monkeypatch.setenv("CMFC_GEMM_SPLITK", str(T))
+        both = _call(gpu, dt, m, m.index("w"), x, N, K)
+        first = _call(gpu, dt, m, m.index("w"), x[:T], N, K)
+        second = _call(gpu, dt, m, m.index("w"), x[T:], N, K)
+        monkeypatch.setenv("CMFC_GEMM_SPLITK", "0")
+        plain = _call(gpu, dt, m, m.index("w"), x, N, K)
+    assert np.array_equal(both[:T], first) and np.array_equal(both[T:], second)
+    assert rel_l2(both, plain) < 5e-6
+    tiles_n, per = N // 256, (T // 256) * (N // 256)
+    differs = 0
+    for tile in range(2 * per):
+        n0, m0 = (tile % tiles_n) * 256, (tile // tiles_n) * 256
+        same = np.array_equal(both[m0:m0 + 256, n0:n0 + 256], plain[m0:m0 + 256, n0:n0 + 256])
+        if tile % per < per // 74 * 74:
+            assert same, tile                     # whole tiles: bit-identical to the unsplit kernel
+        else:
+            differs += not same
+    assert differs > 0                            # the split path really ran, in both prompts
