@@ -508,9 +508,10 @@ void push_ids(std::vector<int>* v, int a, int b, int cc) { v->push_back(a); v->p
 
 // `next` / `next_mods`: the block that follows on the SAME rows (or null); `xn_ready`: the previous
 // call already produced this block's input norm.
+// `rope` holds cos then sin for `rope_rows_n` rows; the block runs on rows [row0, row0 + n) of that table.
 int run_block(Context* c, cmfc_nextdit* d, const DitBlock& b, float* x, int n, const std::vector<int>& segs, const float* mods,
               const DevBuf& rope, size_t rope_rows_n, const DitBlock* next = nullptr, const float* next_mods = nullptr,
-              bool xn_ready = false) {
+              bool xn_ready = false, size_t row0 = 0) {
     BlockMod mod;
     if (b.modulated) {
         mod.s_msa = mods; mod.gate_msa = mods + d->hidden; mod.s_mlp = mods + 2 * d->hidden; mod.gate_mlp = mods + 3 * d->hidden;
@@ -522,8 +523,9 @@ int run_block(Context* c, cmfc_nextdit* d, const DitBlock& b, float* x, int n, c
         ch.next_norm1 = next->bw.norm1;
         ch.next_s_msa = next->modulated ? next_mods : nullptr;
     }
-    return dev_block(c, b.bw, mod, x, n, segs, d->hidden, d->inter, d->nh, d->nkv, d->hd, d->eps, rope.as<float>(),
-                     rope.as<float>() + half, &ch);
+    const size_t at = row0 * (d->hd / 2);
+    return dev_block(c, b.bw, mod, x, n, segs, d->hidden, d->inter, d->nh, d->nkv, d->hd, d->eps, rope.as<float>() + at,
+                     rope.as<float>() + half + at, &ch);
 }
 
 // y = W x + b for a small dense or q8 weight
@@ -656,8 +658,8 @@ int forward_device(Context* c, cmfc_nextdit* d, const float* latents, int batch,
         CMFC_TRY(upload_rope(c, &rope_joint, ids_joint, d->axes));
         d->rope_key[rs] = key.str();
     }
-    // Every prompt of the batch has the same token count, so the GEMMs see a stack of equal periods
-    // and may plan their K split per prompt (a prompt's result must not depend on its batch).
+    // When every sequence of the batch has the same token count the GEMMs see a stack of equal periods
+    // and may plan their K split per sequence (a prompt's result must not depend on its batch).
     struct PeriodGuard {
         Context* c;
         PeriodGuard(Context* c_, int tokens) : c(c_) { c->gemm_period_tokens = tokens; }
@@ -684,13 +686,50 @@ int forward_device(Context* c, cmfc_nextdit* d, const float* latents, int batch,
                 row += n_img;
             }
     }
-    PeriodGuard joint_period(c, n_joint / batch);
-    for (size_t l = 0; l < d->layers.size(); ++l) {
-        const DitBlock* nx = l + 1 < d->layers.size() ? &d->layers[l + 1] : nullptr;
-        CMFC_TRY(run_block(c, d, d->layers[l], xb.as<float>(), n_joint, segs_joint, mods + mk * 4 * hs, rope_joint, (size_t)n_joint,
-                           nx, mods + (mk + 1) * 4 * hs, l > 0));
-        ++mk;
-        if (taps) CMFC_CUDA(cudaMemcpyAsync(taps + l * (size_t)n_joint * hs, xb.p, (size_t)n_joint * hs * 4, cudaMemcpyDeviceToDevice, s));
+    // the period is one SEQUENCE when all sequences have the same length (any launch, whole batch or
+    // half of it, is then a stack of whole periods); with cond and uncond captions of different
+    // lengths there is no common period and the GEMMs are not split
+    bool equal_seqs = true;
+    for (int sl : segs_joint) equal_seqs = equal_seqs && sl == segs_joint[0];
+    PeriodGuard joint_period(c, equal_seqs ? segs_joint[0] : 0);
+    // Sequences never see each other (attention is per segment, everything else per token), so the
+    // batch is cut into two halves that walk the joint layers side by side on two streams: while a
+    // persistent GEMM of one half drains its last, partly empty wave of tiles, the other half's next
+    // kernel takes the free SMs, and a launch gap of one chain is covered by the other.  Results do not
+    // depend on the cut (every kernel's arithmetic is per token or per segment).  CMFC_STREAMS=1 keeps
+    // one chain; the stage profiler (one span per launch group) and the per-layer taps need it too.
+    const char* streams_env = getenv("CMFC_STREAMS");  // read per call
+    const bool two_lanes = segs_joint.size() >= 2 && !c->prof.on && !taps && !(streams_env && atoi(streams_env) == 1);
+    if (two_lanes) {
+        size_t cut = 1;
+        int rows0 = segs_joint[0];
+        while (cut + 1 < segs_joint.size() && 2 * (rows0 + segs_joint[cut]) <= n_joint) rows0 += segs_joint[cut++];
+        const std::vector<int> segs0(segs_joint.begin(), segs_joint.begin() + cut), segs1(segs_joint.begin() + cut, segs_joint.end());
+        const int rows1 = n_joint - rows0;
+        CMFC_CUDA(cudaEventRecord(c->ev_fork, s));
+        CMFC_CUDA(cudaStreamWaitEvent(c->side_stream, c->ev_fork, 0));
+        int rc = OK;
+        for (size_t l = 0; l < d->layers.size() && rc == OK; ++l, ++mk) {
+            const DitBlock* nx = l + 1 < d->layers.size() ? &d->layers[l + 1] : nullptr;
+            rc = run_block(c, d, d->layers[l], xb.as<float>(), rows0, segs0, mods + mk * 4 * hs, rope_joint, (size_t)n_joint, nx,
+                           mods + (mk + 1) * 4 * hs, l > 0, 0);
+            if (rc != OK) break;
+            Lane side(c);
+            rc = run_block(c, d, d->layers[l], xb.as<float>() + (size_t)rows0 * hs, rows1, segs1, mods + mk * 4 * hs, rope_joint,
+                           (size_t)n_joint, nx, mods + (mk + 1) * 4 * hs, l > 0, (size_t)rows0);
+        }
+        // the side chain always rejoins, also after an error: a capture must not end with a forked stream
+        cudaEventRecord(c->ev_join, c->side_stream);
+        cudaStreamWaitEvent(s, c->ev_join, 0);
+        CMFC_TRY(rc);
+    } else {
+        for (size_t l = 0; l < d->layers.size(); ++l) {
+            const DitBlock* nx = l + 1 < d->layers.size() ? &d->layers[l + 1] : nullptr;
+            CMFC_TRY(run_block(c, d, d->layers[l], xb.as<float>(), n_joint, segs_joint, mods + mk * 4 * hs, rope_joint, (size_t)n_joint,
+                               nx, mods + (mk + 1) * 4 * hs, l > 0));
+            ++mk;
+            if (taps) CMFC_CUDA(cudaMemcpyAsync(taps + l * (size_t)n_joint * hs, xb.p, (size_t)n_joint * hs * 4, cudaMemcpyDeviceToDevice, s));
+        }
     }
     // ---- tail: LayerNorm * (1 + scale), project, unpatchify the image tokens ----
     {

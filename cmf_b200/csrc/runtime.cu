@@ -134,6 +134,10 @@ int ctx_set_device(int device) {
         c->device = device;
         c->num_sms = prop.multiProcessorCount;
         CMFC_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+        c->main_stream = c->stream;
+        CMFC_CUDA(cudaStreamCreateWithFlags(&c->side_stream, cudaStreamNonBlocking));
+        CMFC_CUDA(cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming));
+        CMFC_CUDA(cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming));
         CMFC_CUDA(cudaMalloc(&c->status, 4));
         CMFC_CUDA(cudaMemset(c->status, 0, 4));
         CMFC_CUDA(cudaMallocHost(&c->status_host, 4));
@@ -618,7 +622,7 @@ int dev_gemm(Context* c, DevWeight* w, const __nv_bfloat16* x, int M, void* out,
         if (!off && (period > 0 || force)) {
             const size_t need = gemm_pair_splitk_bytes(p, c->num_sms, period);
             if (need) {
-                DevBuf& ws = c->buf("gemm_splitk");
+                DevBuf& ws = c->lane_buf("gemm_splitk");
                 CMFC_TRY(ws.ensure(need));
                 p.splitk_ws = ws.as<float>();
                 p.split_period_tokens = period;
@@ -649,8 +653,9 @@ int prepare_segs(Context* c, const std::vector<int>& segs, SegTable* out) {
         col += (segs[i] + 7) & ~7;
         mx = segs[i] > mx ? segs[i] : mx;
     }
-    if (c->seg_cache.size() >= 8) {  // a forward alternates between two or three segmentations
-        CMFC_CUDA(cudaStreamSynchronize(c->stream));
+    if (c->seg_cache.size() >= 16) {  // a forward alternates between a handful of segmentations
+        CMFC_CUDA(cudaStreamSynchronize(c->main_stream));  // queued kernels of either chain may still read the table
+        CMFC_CUDA(cudaStreamSynchronize(c->side_stream));
         c->seg_cache.front().second.release();
         c->seg_cache.erase(c->seg_cache.begin());
     }
@@ -696,8 +701,8 @@ int dev_block(Context* c, const BlockWeights& bw, const BlockMod& mod, float* x,
     if (st.n_total != n) return fail(ERR_BAD_ARG, "segments do not sum to the token count");
     const int vt_pitch = st.vt_pitch;
     if (!row_cols_supported(hidden)) return fail(ERR_UNSUPPORTED, "hidden size " + std::to_string(hidden) + " is not supported by the row kernels");
-    DevBuf &xn = c->buf("blk_xn"), &qkv = c->buf("blk_qkv"), &qb = c->buf("blk_q"), &kb = c->buf("blk_k"),
-           &vt = c->buf("blk_vt"), &att = c->buf("blk_attn"), &proj = c->buf("blk_proj"), &act = c->buf("blk_act");
+    DevBuf &xn = c->lane_buf("blk_xn"), &qkv = c->lane_buf("blk_qkv"), &qb = c->lane_buf("blk_q"), &kb = c->lane_buf("blk_k"),
+           &vt = c->lane_buf("blk_vt"), &att = c->lane_buf("blk_attn"), &proj = c->lane_buf("blk_proj"), &act = c->lane_buf("blk_act");
     CMFC_TRY(xn.ensure((size_t)n * hidden * 2));
     CMFC_TRY(qkv.ensure((size_t)n * qkv_w * 4));
     CMFC_TRY(qb.ensure((size_t)n * nh * hd * 2));

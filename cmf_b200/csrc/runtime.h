@@ -81,7 +81,13 @@ struct Profile {
 
 struct Context {
     int device = -1;
-    cudaStream_t stream = nullptr;
+    cudaStream_t stream = nullptr;     // every launch goes here ...
+    // ... except while a forward runs two independent halves of its batch side by side: then the
+    // second half's launches go to `side_stream` (Lane swaps it into `stream` while they are
+    // enqueued) and use their own set of block workspaces (lane 1)
+    cudaStream_t main_stream = nullptr, side_stream = nullptr;  // `stream` is one of the two
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    int lane = 0;
     int num_sms = 0;
     uint32_t* status = nullptr;       // device status word for bounded-wait kernels
     uint32_t* status_host = nullptr;  // pinned mirror
@@ -102,6 +108,16 @@ struct Context {
     uint64_t launches = 0;
     Profile prof;
     DevBuf& buf(const std::string& name) { return ws[name]; }
+    // a workspace of the current lane (block-level buffers that two concurrent halves must not share)
+    DevBuf& lane_buf(const std::string& name) { return lane ? ws[name + "#1"] : ws[name]; }
+};
+
+// While alive, launches of the calling thread's context go to the side stream and use lane 1.
+struct Lane {
+    Context* c;
+    cudaStream_t saved;
+    explicit Lane(Context* c_) : c(c_), saved(c_->stream) { c->stream = c->side_stream; c->lane = 1; }
+    ~Lane() { c->stream = saved; c->lane = 0; }
 };
 
 const std::string& last_error();

@@ -65,19 +65,33 @@ def test_lumina_1024_pair_single_and_batch_consistency(tmp_path, monkeypatch):
         both = denoise(dit, lat, cap, cap_u, p)
         one = denoise(dit, lat[1:2], cap[1:2], cap_u[1:2], p)
         assert rel_l2(one[0], both[1]) < 1e-5                # a prompt's result does not depend on its batch
-        # The feed-forward down projection (K = 9216; 306 tiles per prompt on 74 CTA pairs) runs with
-        # the last 10 tiles of EVERY prompt cut along K; the plan depends on the position inside the
-        # prompt only, which is what keeps the line above true.  Without the split: one launch less
-        # per joint block (the kernel that adds the slices), the same result up to f32 summation order.
+        # The feed-forward down projection (K = 9216; 153 tiles per 4352-token sequence on 74 CTA pairs)
+        # runs with the last 5 tiles of EVERY sequence cut along K; the plan depends on the position
+        # inside the sequence only, which is what keeps the line above true.  Without the split: one
+        # launch less per down projection (the kernel that adds the slices), the same result up to f32
+        # summation order.  The forward walks the joint layers as two side-by-side chains (one per
+        # sequence here), so there are 2 x 26 down projections; as one chain (CMFC_STREAMS=1) 26 --
+        # and the very same bits, since no kernel's arithmetic depends on how the batch is cut.
         from cmf_b200 import gpu
         gpu.launch_count(reset=True)
-        pc2, _ = dit.forward_cfg_pair(lat[0], 128, 128, cc, 256, cu, 256, 0.5)
+        pc2, pu2 = dit.forward_cfg_pair(lat[0], 128, 128, cc, 256, cu, 256, 0.5)
         with_split = gpu.launch_count(reset=True)
         monkeypatch.setenv("CMFC_GEMM_SPLITK", "0")
         pc3, _ = dit.forward_cfg_pair(lat[0], 128, 128, cc, 256, cu, 256, 0.5)
         without = gpu.launch_count(reset=True)
         monkeypatch.delenv("CMFC_GEMM_SPLITK")
         assert np.array_equal(pc, pc2)
-        assert with_split - without == 26, (with_split, without)
-        assert rel_l2(pc2, pc3) < 2e-3, rel_l2(pc2, pc3)
+        assert with_split - without == 52, (with_split, without)
+        # (last-bit differences of one GEMM grow through 26 blocks of bf16 operand rounding; the pair
+        # path against two single forwards, above, is held to the same 5e-3)
+        assert 0 < rel_l2(pc2, pc3) < 5e-3, rel_l2(pc2, pc3)
+        monkeypatch.setenv("CMFC_STREAMS", "1")
+        pc4, pu4 = dit.forward_cfg_pair(lat[0], 128, 128, cc, 256, cu, 256, 0.5)
+        one_chain = gpu.launch_count(reset=True)
+        monkeypatch.setenv("CMFC_GEMM_SPLITK", "0")
+        dit.forward_cfg_pair(lat[0], 128, 128, cc, 256, cu, 256, 0.5)
+        assert one_chain - gpu.launch_count(reset=True) == 26
+        monkeypatch.delenv("CMFC_GEMM_SPLITK")
+        monkeypatch.delenv("CMFC_STREAMS")
+        assert np.array_equal(pc2, pc4) and np.array_equal(pu2, pu4)
         dit.close()
