@@ -6,7 +6,10 @@
 // One CTA owns 256 queries of one (segment, head): two 128-row query tiles A and B that share
 // every K / V^T tile brought in by TMA.  Per key tile of 128:
 //   S = Q K^T      tcgen05.mma, Q and K from shared memory (64-byte swizzle atoms of 32 dims,
-//                  so head_dim 96 needs no padding), 128 x 128 f32 into TMEM
+//                  so head_dim 96 needs no padding), 128 x 128 f32 into TMEM.  Inside a NextDiT
+//                  block the query tiles are built in the kernel's prologue from the raw f32
+//                  projection (head RMS norm + 2-D RoPE, see the softmax warps); the facade entry
+//                  passes finished bf16 rows, which arrive by TMA like K
 //   softmax        four warps per query tile, one query row per thread: tcgen05.ld the row,
 //                  running max / sum in the exp2 domain, P packed to bf16 and written back
 //                  over the S columns with tcgen05.st
@@ -91,8 +94,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     volatile uint32_t* abort_flag = &bars->abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+    const bool q_prologue = p.q_raw != nullptr;  // the softmax warps build the query tiles themselves
     if (threadIdx.x == 0) {
-        mbar_init(&bars->q_full, 1);
+        mbar_init(&bars->q_full, q_prologue ? 8 : 1);
         for (int s = 0; s < KV_STAGES; ++s) {
             mbar_init(&bars->k_full[s], 1);
             // split plan: each tile has its own MMA warp, and both must be done with a stage
@@ -126,11 +130,13 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (elect_one()) {
-            mbar_expect_tx(&bars->q_full, 2 * L::Q_TILE);
-            for (int t = 0; t < 2; ++t)
-                for (int a = 0; a < L::ATOMS; ++a)
-                    tma_load_2d(q_smem + t * L::Q_TILE + a * QT * 64, &tm_q, &bars->q_full, head * HD + 32 * a,
-                                seg0 + q0 + t * QT);
+            if (!q_prologue) {
+                mbar_expect_tx(&bars->q_full, 2 * L::Q_TILE);
+                for (int t = 0; t < 2; ++t)
+                    for (int a = 0; a < L::ATOMS; ++a)
+                        tma_load_2d(q_smem + t * L::Q_TILE + a * QT * 64, &tm_q, &bars->q_full, head * HD + 32 * a,
+                                    seg0 + q0 + t * QT);
+            }
             for (int j = 0; j < nk; ++j) {
                 const int s = j % KV_STAGES;
                 const uint32_t ph = (j / KV_STAGES) & 1u;
@@ -251,6 +257,53 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         const float c = p.scale * 1.4426950408889634f;  // softmax in the exp2 domain
         float m_ref = -INFINITY, l_run = 0.0f;
         bool ok = true;
+        if (q_prologue) {
+            // Prologue: this thread's query row from the raw f32 projection -> per-head RMS norm
+            // (eps 1e-5; crates/cortiq-engine/src/dit.rs:1078-1102) -> interleaved-pair rotation ->
+            // bf16, written where the TMA load would have put it: atoms of 32 dims, 64 bytes per row,
+            // 16-byte chunks XOR-ed with address bits [7, 9) (the 64-byte swizzle).  Same arithmetic
+            // as qk_rope_kernel, which still prepares K (a K tile is read by every query tile of its
+            // three query heads; rotating it here would repeat the work 51 times at 4352 tokens).
+            const int q = q0 + t * QT + row;
+            uint8_t* qrow = q_smem + t * L::Q_TILE + row * 64;
+            const int swz = (row >> 1) & 3;
+            if (q < seg_len) {
+                const size_t tok = (size_t)(seg0 + q);
+                const float4* src = reinterpret_cast<const float4*>(p.q_raw + tok * p.ld_q + (size_t)head * HD);
+                const float4* ct = reinterpret_cast<const float4*>(p.cos_t + tok * (HD / 2));
+                const float4* st = reinterpret_cast<const float4*>(p.sin_t + tok * (HD / 2));
+                const float4* wq = reinterpret_cast<const float4*>(p.norm_q);
+                float4 x[HD / 4];
+#pragma unroll
+                for (int i = 0; i < HD / 4; ++i) x[i] = src[i];
+                double ss = 0.0;
+#pragma unroll
+                for (int i = 0; i < HD / 4; ++i) ss += sq4(x[i]);
+                const float inv = (float)(1.0 / sqrt(ss / HD + 1e-5));
+                auto rot = [&](float a0, float a1, float g0, float g1, float cs, float sn) {
+                    const float a = rms_elem(a0, inv, g0), b = rms_elem(a1, inv, g1);
+                    return pack_bf16(fmaf(a, cs, -(b * sn)), fmaf(a, sn, b * cs));
+                };
+#pragma unroll
+                for (int k = 0; k < HD / 8; ++k) {  // eight dims = four rotation pairs = one 16-byte chunk
+                    const float4 g0 = __ldg(wq + 2 * k), g1 = __ldg(wq + 2 * k + 1);
+                    const float4 cs = ct[k], sn = st[k];
+                    uint4 o;
+                    o.x = rot(x[2 * k].x, x[2 * k].y, g0.x, g0.y, cs.x, sn.x);
+                    o.y = rot(x[2 * k].z, x[2 * k].w, g0.z, g0.w, cs.y, sn.y);
+                    o.z = rot(x[2 * k + 1].x, x[2 * k + 1].y, g1.x, g1.y, cs.z, sn.z);
+                    o.w = rot(x[2 * k + 1].z, x[2 * k + 1].w, g1.z, g1.w, cs.w, sn.w);
+                    *reinterpret_cast<uint4*>(qrow + (k >> 2) * (QT * 64) + (((k & 3) ^ swz) << 4)) = o;
+                }
+            } else {
+#pragma unroll
+                for (int k = 0; k < HD / 8; ++k)
+                    *reinterpret_cast<uint4*>(qrow + (k >> 2) * (QT * 64) + (((k & 3) ^ swz) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+            }
+            fence_proxy_async_smem();  // generic-proxy writes, read by the tensor core through the async proxy
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->q_full);
+        }
         for (int j = 0; j < nk; ++j) {
             if (!mbar_wait<60>(&bars->s_full[t], j & 1u, abort_flag, 19)) { ok = false; break; }
             tc_fence_after();

@@ -336,6 +336,18 @@ __device__ __forceinline__ void ex2_poly_x2(float t0, float t1, float& e0, float
     e1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(r1) << 23));
 }
 
+// Row statistics: the squares of four neighbouring values are summed in f32 (relative error
+// below 2^-22) and those partial sums are accumulated in f64 across the row and the warp; the
+// reciprocal root is taken in f64 and rounded once to f32.  The reference keeps every square and
+// the scaling product in f64 (dit.rs:269-275); the difference, about 1e-7 relative per element, is
+// far below the bf16 rounding of the GEMM operands that follows, and conversions between f32 and
+// f64 (16 per clock per SM) no longer bound these kernels.
+__device__ __forceinline__ double sq4(const float4& v) {
+    return (double)fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, v.w * v.w)));
+}
+// rms(v; w, eps) element: (v * inv) * w
+__device__ __forceinline__ float rms_elem(float v, float inv, float w) { return (v * inv) * w; }
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

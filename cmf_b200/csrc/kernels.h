@@ -62,6 +62,15 @@ struct AttnParams {
     float scale;             // 1/sqrt(hd)
     __nv_bfloat16* out;      // [n_total, nh*hd]
     uint32_t* status;
+    // Prologue form (q_raw != nullptr): the query tiles are not fetched as finished bf16 rows by TMA;
+    // the kernel reads the raw f32 projection rows q_raw [n_total, ld_q] (head h at column h*hd),
+    // applies the per-head RMS norm (eps 1e-5, weight norm_q [hd]) and the interleaved-pair rotation
+    // with cos / sin [n_total, hd/2] f32, and writes the bf16 tile into shared memory itself.
+    const float* q_raw = nullptr;
+    int ld_q = 0;
+    const float* norm_q = nullptr;
+    const float* cos_t = nullptr;
+    const float* sin_t = nullptr;
 };
 int attn_smem_bytes(int hd);
 int launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_vt,
@@ -101,6 +110,7 @@ void launch_residual_then_norm(float* x, const float* src, const float* w_res, c
                                __nv_bfloat16* out_bf16, cudaStream_t s);
 // per (token, head): qk RMS norm (eps 1e-5) + interleaved-pair RoPE (cos / sin [n, hd/2] f32); writes Q, K bf16
 // token-major (V never passes through here: the QKV GEMM's epilogue writes V^T itself)
+// q == nullptr: only the K heads (the attention kernel then normalises and rotates Q in its prologue)
 void launch_qk_rope_pack(const float* qkv, int n, int nh, int nkv, int hd, const float* norm_q,
                          const float* norm_k, const float* cos_t, const float* sin_t, __nv_bfloat16* q,
                          __nv_bfloat16* k, cudaStream_t s);

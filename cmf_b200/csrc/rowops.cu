@@ -22,18 +22,6 @@ __device__ __forceinline__ void st_bf16x4(__nv_bfloat16* p, float a, float b, fl
     *reinterpret_cast<uint2*>(p) = v;
 }
 
-// Row statistics: the squares of four neighbouring values are summed in f32 (relative error
-// below 2^-22) and those partial sums are accumulated in f64 across the row and the warp; the
-// reciprocal root is taken in f64 and rounded once to f32.  The reference keeps every square and
-// the scaling product in f64 (dit.rs:269-275); the difference, about 1e-7 relative per element, is
-// far below the bf16 rounding of the GEMM operands that follows, and conversions between f32 and
-// f64 (16 per clock per SM) no longer bound these kernels.
-__device__ __forceinline__ double sq4(const float4& v) {
-    return (double)fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, v.w * v.w)));
-}
-// rms(v; w, eps) element: (v * inv) * w
-__device__ __forceinline__ float rms_elem(float v, float inv, float w) { return (v * inv) * w; }
-
 template <int NV>  // float4 per lane; cols = 128 * NV
 __global__ void __launch_bounds__(32 * ROW_WARPS)
 rms_mod_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ shift,
@@ -197,12 +185,13 @@ qk_rope_kernel(const float* __restrict__ qkv, int n, int nh, int nkv, const floa
                const float* __restrict__ norm_k, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_out) {
     constexpr int hd = 32 * PPL;
-    const int heads = nh + nkv;
+    const int h_first = q_out ? 0 : nh;  // without a Q output only the K heads are walked
+    const int heads = nh + nkv - h_first;
     const long item = (long)blockIdx.x * (ROPE_THREADS / 4) + (threadIdx.x >> 2);
     const int l = threadIdx.x & 3;
     const bool active = item < (long)n * heads;
     const int tok = active ? (int)(item / heads) : 0;
-    const int h = active ? (int)(item % heads) : 0;
+    const int h = h_first + (active ? (int)(item % heads) : 0);
     const bool is_q = h < nh;
     const int ld_in = (nh + 2 * nkv) * hd;
     const float* src = qkv + (size_t)tok * ld_in + (size_t)h * hd + l * 8;  // q heads then k heads are contiguous
@@ -498,7 +487,7 @@ bool row_cols_supported(int cols) {
 void launch_qk_rope_pack(const float* qkv, int n, int nh, int nkv, int hd, const float* norm_q,
                          const float* norm_k, const float* cos_t, const float* sin_t, __nv_bfloat16* q,
                          __nv_bfloat16* k, cudaStream_t s) {
-    const long items = (long)n * (nh + nkv);
+    const long items = (long)n * ((q ? nh : 0) + nkv);
     const int grid = (int)((items + ROPE_THREADS / 4 - 1) / (ROPE_THREADS / 4));
     switch (hd / 32) {
         case 1: qk_rope_kernel<1><<<grid, ROPE_THREADS, 0, s>>>(qkv, n, nh, nkv, norm_q, norm_k, cos_t, sin_t, q, k); break;

@@ -143,8 +143,16 @@ struct GemmVt {
 int dev_gemm(Context* c, DevWeight* w, const __nv_bfloat16* x, int M, void* out, int ldo, int mode,
              const GemmVt* vt = nullptr);
 int prepare_segs(Context* c, const std::vector<int>& segs, SegTable* out);
+// raw (optional): the queries come as the raw f32 projection and are normalised and rotated in the
+// kernel's prologue (AttnParams::q_raw); q is then only a placeholder for the tensor map
+struct AttnRawQ {
+    const float* q_raw;
+    int ld_q;
+    const float *norm_q, *cos_t, *sin_t;
+};
 int dev_attention(Context* c, const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* vt,
-                  const SegTable& st, int nh, int nkv, int hd, float scale, __nv_bfloat16* out);
+                  const SegTable& st, int nh, int nkv, int hd, float scale, __nv_bfloat16* out,
+                  const AttnRawQ* raw = nullptr);
 
 struct BlockWeights {
     DevWeight *qkv = nullptr, *o = nullptr, *w13 = nullptr, *w2 = nullptr;

@@ -84,9 +84,12 @@ def test_euler_30_steps_tiny(tmp_path):
     assert rel_l2(got[0], want) < TOL
 
 
-def test_euler_8_steps_lumina_width_4_layers(tmp_path):
-    """Eight CFG Euler steps at hidden 2304 (4 joint + 1 + 1 refiner layers, q4_tiled), 32x32 latent."""
+@pytest.mark.parametrize("prologue", ["0", "1"])
+def test_euler_8_steps_lumina_width_4_layers(tmp_path, monkeypatch, prologue):
+    """Eight CFG Euler steps at hidden 2304 (4 joint + 1 + 1 refiner layers, q4_tiled), 32x32 latent;
+    with the separate qk-norm + RoPE pass and with Q rotated in the attention prologue (head_dim 96)."""
     from cmf_b200 import GenParams, Model, NextDit, denoise, synth
+    monkeypatch.setenv("CMFC_ROPE_PROLOGUE", prologue)
     cfg = dict(synth.LUMINA2, num_layers=4, num_refiner_layers=1)
     path = os.path.join(str(tmp_path), "l4.cmf")
     synth.write_model(path, cfg, attn="q4t", ffn="q4t", seed=3)

@@ -132,8 +132,12 @@ def test_tiny_forward_pair_per_block_and_latent(tmp_path, plan_name):
         dit.close()
 
 
-def test_ragged_forward(tmp_path):
+@pytest.mark.parametrize("prologue", ["0", "1"])
+def test_ragged_forward(tmp_path, monkeypatch, prologue):
+    """Ragged latent and caption lengths; once with the separate qk-norm + RoPE pass for Q and K, once
+    with Q normalised and rotated in the attention kernel's prologue (CMFC_ROPE_PROLOGUE=1)."""
     from cmf_b200 import Model, NextDit
+    monkeypatch.setenv("CMFC_ROPE_PROLOGUE", prologue)
     cfg = synth.TINY
     path = str(tmp_path / "m.cmf")
     tensors, _ = build(cfg, path, synth.quant_plan(cfg, oc.Q8_ROW, oc.Q4TP), seed=5, norm_jitter=0.1, std=0.05)
