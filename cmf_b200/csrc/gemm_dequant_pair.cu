@@ -44,7 +44,8 @@ constexpr int NUM_DQ_WARPS = 8;     // dequant warps per k-block
 constexpr int DQ_GROUPS = 2;        // groups of dequant warps taking k-blocks in turn
 constexpr int NUM_EPI_WARPS = 8;
 constexpr int THREADS = 32 * (2 + DQ_GROUPS * NUM_DQ_WARPS + NUM_EPI_WARPS);
-constexpr int SMEM_BYTES = STAGES * (X_STAGE + W_STAGE + S_STAGE) + 1024 + 512;
+constexpr int GLU_STAGE = 32 * 16 * 2;  // one epilogue warp's staged chunk: 32 tokens x 16 channels bf16
+constexpr int SMEM_BYTES = STAGES * (X_STAGE + W_STAGE + S_STAGE) + NUM_EPI_WARPS * GLU_STAGE + 1024 + 512;
 constexpr uint32_t PEER_MASK = 0xFEFFFFFFu;  // clears the CTA-rank bit of a shared::cluster address: the even CTA
 
 struct Bars {
@@ -148,13 +149,15 @@ __device__ __forceinline__ bool unit_at(int i, int pair, int pairs, int tiles, i
 template <int WKIND>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_dequant_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
-                         const __grid_constant__ CUtensorMap tm_s, GemmParams p, SplitPlan sp) {
+                         const __grid_constant__ CUtensorMap tm_s, const __grid_constant__ CUtensorMap tm_o, GemmParams p,
+                         SplitPlan sp) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* x_smem = smem;
     uint8_t* w_smem = smem + STAGES * X_STAGE;
     uint8_t* s_smem = w_smem + STAGES * W_STAGE;
-    Bars* bars = reinterpret_cast<Bars*>(s_smem + STAGES * S_STAGE);
+    uint8_t* glu_smem = s_smem + STAGES * S_STAGE;
+    Bars* bars = reinterpret_cast<Bars*>(glu_smem + NUM_EPI_WARPS * GLU_STAGE);
     volatile uint32_t* abort_flag = &bars->abort_flag;
     cg::cluster_group cluster = cg::this_cluster();
     const int rank = (int)cluster.block_rank();   // 0: even CTA (issues the MMAs), 1: odd CTA
@@ -186,6 +189,7 @@ gemm_dequant_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
         tma_prefetch_desc(&tm_x);
         tma_prefetch_desc(&tm_w);
         if (WKIND != 0) tma_prefetch_desc(&tm_s);
+        if (p.tma_out) tma_prefetch_desc(&tm_o);
     }
     if (warp == 1) {
         tmem_alloc_pair(&bars->tmem_base, TMEM_COLS);
@@ -321,6 +325,17 @@ gemm_dequant_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
         const int ehalf = (warp - 2 - DQ_GROUPS * NUM_DQ_WARPS) >> 2;
         const int row = quarter * 32 + lane;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        // Staged output of the fused SwiGLU / GeGLU modes: the 32 tokens x 16 channels (bf16) a chunk
+        // yields go to this warp's 1 KiB of shared memory, one `st.shared` per value at a fixed offset,
+        // and one lane hands the box to a TMA store, which also clips the rows past M.  The kernel is
+        // bound by instruction issue (with the epilogue's work removed the K = 2304 GEMMs run at
+        // 1590-1650 TFLOP/s): address arithmetic, predicates and scattered 2-byte global stores were a
+        // third of this epilogue's instructions.  The f32 modes store directly: staging them was
+        // measured and changes nothing (their cost is the 128 KB per tile that has to leave through the
+        // load/store path either way).
+        const int epi = warp - 2 - DQ_GROUPS * NUM_DQ_WARPS;
+        __nv_bfloat16* stage_bf = reinterpret_cast<__nv_bfloat16*>(glu_smem + epi * GLU_STAGE);
+        bool store_pending = false;  // lane 0: a bulk store of this warp may still be reading the stage
         uint32_t tile_i = 0;
         Unit u;
         for (int ui = 0; unit_at(ui, pair, pairs, tiles, kblocks, sp, u) && !*abort_flag; ++ui, ++tile_i) {
@@ -334,6 +349,55 @@ gemm_dequant_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
             auto emit = [&](const uint32_t (&v)[32], int c) {
                 const int mb = m0 + c * 32;
                 if (mb >= p.M) return;
+                if (p.tma_out) {  // SwiGLU / GeGLU, staged (whole tiles only: these modes are never K-split)
+                    if (store_pending) bulk_wait_group_read0();
+                    __syncwarp();
+                    // gate / up of a channel in adjacent lanes (W1 / W3 rows interleaved): the lanes swap one
+                    // value per token pair; the even lane finishes token j, the odd lane token j + 1
+                    const bool odd = lane & 1;
+                    const bool gelu = p.mode == GEMM_OUT_GEGLU;
+                    __nv_bfloat16* dst = stage_bf + (odd ? 16 : 0) + (lane >> 1);
+                    if (gelu) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 2) {
+                            float mine_a = __uint_as_float(v[j]), mine_b = __uint_as_float(v[j + 1]);
+                            if (WKIND == 0) { mine_a *= rs; mine_b *= rs; }
+                            const float got = __shfl_xor_sync(0xffffffffu, odd ? mine_a : mine_b, 1);
+                            const float g = odd ? got : mine_a;
+                            const float u_ = odd ? mine_b : got;
+                            dst[j * 16] = __float2bfloat16_rn(gelu_tanh_f(g) * u_);
+                        }
+                    } else {
+                        // two token pairs per step, the arithmetic of silu(g) * u as packed f32x2 operations
+                        const uint64_t half2 = pack_f32x2(0.5f, 0.5f);
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            float a0 = __uint_as_float(v[j]), b0 = __uint_as_float(v[j + 1]);
+                            float a1 = __uint_as_float(v[j + 2]), b1 = __uint_as_float(v[j + 3]);
+                            if (WKIND == 0) { a0 *= rs; b0 *= rs; a1 *= rs; b1 *= rs; }
+                            const float got0 = __shfl_xor_sync(0xffffffffu, odd ? a0 : b0, 1);
+                            const float got1 = __shfl_xor_sync(0xffffffffu, odd ? a1 : b1, 1);
+                            const uint64_t g2 = pack_f32x2(odd ? got0 : a0, odd ? got1 : a1);
+                            const uint64_t u2 = pack_f32x2(odd ? b0 : got0, odd ? b1 : got1);
+                            float h0, h1, t0, t1, r0, r1;
+                            unpack_f32x2(mul_f32x2(g2, half2), h0, h1);
+                            asm("tanh.approx.f32 %0, %1;" : "=f"(t0) : "f"(h0));
+                            asm("tanh.approx.f32 %0, %1;" : "=f"(t1) : "f"(h1));
+                            const uint64_t sg2 = fma_f32x2(pack_f32x2(t0, t1), half2, half2);  // sigmoid(g) = 0.5 tanh(g / 2) + 0.5
+                            unpack_f32x2(mul_f32x2(mul_f32x2(g2, sg2), u2), r0, r1);
+                            dst[j * 16] = __float2bfloat16_rn(r0);
+                            dst[(j + 2) * 16] = __float2bfloat16_rn(r1);
+                        }
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&tm_o, stage_bf, (n0 + quarter * 32) >> 1, mb);
+                        bulk_commit_group();
+                        store_pending = true;
+                    }
+                    return;
+                }
                 if (u.slot >= 0) {
                     // K slice of a tile: partial sums, [token in tile][row in tile]
                     float* out = p.splitk_ws + ((size_t)u.slot * TT + c * 32) * (2 * TW) + rank * TW + row;
@@ -385,6 +449,7 @@ gemm_dequant_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                 emit(va, c0 + i);
             }
         }
+        if (store_pending) bulk_wait_group0();  // the staged stores have left shared memory and completed
     }
 
     // ---------------- common exit ----------------
@@ -457,7 +522,7 @@ size_t gemm_pair_splitk_bytes(const GemmParams& p, int num_sms, int period_token
 }
 
 int launch_gemm_dequant_pair(int wkind, const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUtensorMap& tm_s,
-                             const GemmParams& p, int num_sms, cudaStream_t stream) {
+                             const CUtensorMap& tm_out, const GemmParams& p, int num_sms, cudaStream_t stream) {
     if (!gemm_pair_supported(p)) return fail(ERR_SHAPE, "pair GEMM needs K % 64 == 0 and N % 256 == 0");
     static std::atomic<bool> configured[3][64];
     auto kern = wkind == 0 ? gemm_dequant_pair_kernel<0> : (wkind == 1 ? gemm_dequant_pair_kernel<1> : gemm_dequant_pair_kernel<2>);
@@ -484,7 +549,7 @@ int launch_gemm_dequant_pair(int wkind, const CUtensorMap& tm_x, const CUtensorM
     cfg.numAttrs = 1;
     SplitPlan sp = {1, 0, 0, 0};
     if (p.splitk_ws) sp = plan_split(p, pairs, p.split_period_tokens);
-    CMFC_CUDA(cudaLaunchKernelEx(&cfg, kern, tm_x, tm_w, tm_s, p, sp));
+    CMFC_CUDA(cudaLaunchKernelEx(&cfg, kern, tm_x, tm_w, tm_s, tm_out, p, sp));
     if (sp.splits > 1) {
         gemm_splitk_reduce_kernel<<<dim3(sp.periods * (sp.period - sp.whole), TT / 16), 256, 0, stream>>>(
             p.splitk_ws, sp, p.N / (2 * TW), p.M, reinterpret_cast<float*>(p.out), p.ldo);

@@ -26,6 +26,9 @@ struct GemmParams {
     // launch is a stack of equal prompts (each a multiple of 256 tokens), 0 = the launch is one period.
     float* splitk_ws = nullptr;
     int split_period_tokens = 0;
+    // pair kernel, SwiGLU / GeGLU modes: the epilogue stages each chunk in shared memory and a TMA store
+    // writes it out (tm_out of launch_gemm_dequant_pair: bf16 [M, N/2], boxes of 32 tokens x 16 channels)
+    int tma_out = 0;
     // f32 output of a fused QKV projection: weight rows >= vt_row0 are V channels and are written
     // as bf16 rows of V^T [N - vt_row0, vt_pitch] instead (token m of segment z at column
     // seg_table[nseg + 1 + z] + m - seg_table[z]); the f32 columns of those rows are left untouched.
@@ -49,7 +52,8 @@ int gemm_pair_tile_tokens();
 // bytes of GemmParams::splitk_ws this launch would use (0: the launch is not split)
 size_t gemm_pair_splitk_bytes(const GemmParams& p, int num_sms, int period_tokens);
 int launch_gemm_dequant_pair(int wkind, const CUtensorMap& tm_x, const CUtensorMap& tm_w, const CUtensorMap& tm_s,
-                             const GemmParams& p, int num_sms, cudaStream_t stream);
+                             const CUtensorMap& tm_out, const GemmParams& p, int num_sms, cudaStream_t stream);
+
 
 // ---------------- flash attention (attention.cu) ----------------
 struct AttnParams {

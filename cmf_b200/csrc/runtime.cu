@@ -634,7 +634,16 @@ int dev_gemm(Context* c, DevWeight* w, const __nv_bfloat16* x, int M, void* out,
     CMFC_TRY(make_tensor_map_2d(&tm_x, x, 2, (uint64_t)M, (uint64_t)w->cols, (uint64_t)w->cols * 2,
                                 pair ? gemm_pair_tile_tokens() : gemm_tile_tokens(), 64, 3));
     c->launches++;
-    if (pair) return launch_gemm_dequant_pair(wkind, tm_x, w->tm_w, w->tm_s, p, c->num_sms, c->stream);
+    if (pair) {
+        // the fused SwiGLU / GeGLU output leaves through staged TMA stores when the matrix can be
+        // described by a tensor map (16-byte aligned base and pitch)
+        CUtensorMap tm_o = tm_x;
+        if ((mode == GEMM_OUT_SWIGLU || mode == GEMM_OUT_GEGLU) && !(reinterpret_cast<uintptr_t>(out) & 15) && ldo % 8 == 0) {
+            CMFC_TRY(make_tensor_map_2d(&tm_o, out, 2, (uint64_t)M, (uint64_t)w->rows / 2, (uint64_t)ldo * 2, 32, 16, 0));
+            p.tma_out = 1;
+        }
+        return launch_gemm_dequant_pair(wkind, tm_x, w->tm_w, w->tm_s, tm_o, p, c->num_sms, c->stream);
+    }
     return launch_gemm_dequant(wkind, tm_x, w->tm_w, w->tm_s, p, c->num_sms, c->stream);
 }
 
