@@ -206,8 +206,10 @@ extern "C" int cmfc_dit_attention(const float* qh, const float* kh, const float*
     launch_transpose_head_major(d_in + qn, (int)nkv, (int)n, (int)hd, 1.0f, kb.as<__nv_bfloat16>(), c->stream);
     launch_v_head_major_to_vt(d_in + qn + kn, (int)nkv, (int)n, (int)hd, vt.as<__nv_bfloat16>(), st.vt_pitch, c->stream);
     c->launches += 3;
+    float score_ref = 0.0f;
+    CMFC_TRY(attention_score_ref(c, qb.as<__nv_bfloat16>(), kb.as<__nv_bfloat16>(), n, (int)nh, (int)nkv, (int)hd, scale, &score_ref));
     CMFC_TRY(dev_attention(c, qb.as<__nv_bfloat16>(), kb.as<__nv_bfloat16>(), vt.as<__nv_bfloat16>(), st, (int)nh, (int)nkv,
-                           (int)hd, scale, ob.as<__nv_bfloat16>()));
+                           (int)hd, scale, ob.as<__nv_bfloat16>(), nullptr, score_ref));
     launch_bf16_to_f32(ob.as<__nv_bfloat16>(), of.as<float>(), qn, c->stream);
     c->launches++;
     CMFC_CUDA(cudaMemcpyAsync(out, of.p, qn * 4, cudaMemcpyDeviceToHost, c->stream));
@@ -293,6 +295,11 @@ extern "C" int cmfc_dit_block_seg(cmfc_model* m, const cmfc_dit_block_args* a, c
     CMFC_TRY(st.commit());
     bw.norm1 = st.at<float>(o_n1); bw.norm2 = st.at<float>(o_n2); bw.ffn_norm1 = st.at<float>(o_f1); bw.ffn_norm2 = st.at<float>(o_f2);
     bw.norm_q = st.at<float>(o_nq); bw.norm_k = st.at<float>(o_nk);
+    {
+        float gq = 0.0f, gk = 0.0f;
+        for (size_t i = 0; i < a->hd; ++i) { gq = fmaxf(gq, fabsf(a->norm_q[i])); gk = fmaxf(gk, fabsf(a->norm_k[i])); }
+        bw.qk_gain = gq * gk;
+    }
     BlockMod mod;
     if (modulated) { mod.s_msa = st.at<float>(o_sm); mod.gate_msa = st.at<float>(o_gm); mod.s_mlp = st.at<float>(o_sl); mod.gate_mlp = st.at<float>(o_gl); }
     if (!a->resident_in) {
@@ -456,6 +463,15 @@ int load_block(Context* c, cmfc_nextdit* d, const std::string& p, bool modulated
     CMFC_TRY(dense_f32(c, m, p + ".ffn_norm2.weight", &b->bw.ffn_norm2));
     CMFC_TRY(dense_f32(c, m, p + ".attn.norm_q.weight", &b->bw.norm_q));
     CMFC_TRY(dense_f32(c, m, p + ".attn.norm_k.weight", &b->bw.norm_k));
+    {
+        const int hd = d->hd;
+        std::vector<float> g(2 * (size_t)hd);
+        CMFC_CUDA(cudaMemcpy(g.data(), b->bw.norm_q, hd * sizeof(float), cudaMemcpyDeviceToHost));
+        CMFC_CUDA(cudaMemcpy(g.data() + hd, b->bw.norm_k, hd * sizeof(float), cudaMemcpyDeviceToHost));
+        float gq = 0.0f, gk = 0.0f;
+        for (int i = 0; i < hd; ++i) { gq = fmaxf(gq, fabsf(g[i])); gk = fmaxf(gk, fabsf(g[hd + i])); }
+        b->bw.qk_gain = gq * gk;
+    }
     if (modulated) {
         const int64_t im = need(p + ".norm1.linear.weight");
         if (im < 0) return fail(ERR_NOT_FOUND, "block " + p + " is missing its modulation linear");
@@ -1160,14 +1176,16 @@ extern "C" int cmfc_bench_attention(size_t nh, size_t nkv, size_t hd, size_t n, 
     launch_f32_to_bf16(f.as<float>(), v.as<__nv_bfloat16>(), vn, c->stream);
     c->launches += 6;
     const float scale = 1.0f / sqrtf((float)hd);
+    float score_ref = 0.0f;  // the form a NextDiT block launches: the reference known in advance
+    CMFC_TRY(attention_score_ref(c, q.as<__nv_bfloat16>(), k.as<__nv_bfloat16>(), tot, (int)nh, (int)nkv, (int)hd, scale, &score_ref));
     for (int i = 0; i < 3; ++i)
-        CMFC_TRY(dev_attention(c, q.as<__nv_bfloat16>(), k.as<__nv_bfloat16>(), v.as<__nv_bfloat16>(), st, (int)nh, (int)nkv, (int)hd, scale, o.as<__nv_bfloat16>()));
+        CMFC_TRY(dev_attention(c, q.as<__nv_bfloat16>(), k.as<__nv_bfloat16>(), v.as<__nv_bfloat16>(), st, (int)nh, (int)nkv, (int)hd, scale, o.as<__nv_bfloat16>(), nullptr, score_ref));
     cudaEvent_t e0, e1;
     CMFC_CUDA(cudaEventCreate(&e0));
     CMFC_CUDA(cudaEventCreate(&e1));
     CMFC_CUDA(cudaEventRecord(e0, c->stream));
     for (int i = 0; i < iters; ++i)
-        CMFC_TRY(dev_attention(c, q.as<__nv_bfloat16>(), k.as<__nv_bfloat16>(), v.as<__nv_bfloat16>(), st, (int)nh, (int)nkv, (int)hd, scale, o.as<__nv_bfloat16>()));
+        CMFC_TRY(dev_attention(c, q.as<__nv_bfloat16>(), k.as<__nv_bfloat16>(), v.as<__nv_bfloat16>(), st, (int)nh, (int)nkv, (int)hd, scale, o.as<__nv_bfloat16>(), nullptr, score_ref));
     CMFC_CUDA(cudaEventRecord(e1, c->stream));
     CMFC_CUDA(cudaEventSynchronize(e1));
     float ms = 0;

@@ -70,8 +70,10 @@ struct AttnSmem {
     static constexpr int TOTAL = 2 * Q_TILE + KV_STAGES * (K_TILE + V_TILE) + 1024 + 256;
 };
 
-// POLY_OF_8: pairs out of every eight whose exp2 runs on the FMA pipe instead of the special-function unit
-template <int HD, int POLY_OF_8>
+// POLY_OF_8: pairs out of every eight whose exp2 runs on the FMA pipe instead of the special-function unit.
+// FIXED: every score of the launch is known to stay below p.score_ref (log2 units, see AttnParams), which
+// then is the reference of every row from the first key tile on: no row maximum, no rescaling of O.
+template <int HD, int POLY_OF_8, bool FIXED>
 __global__ void __launch_bounds__(ATTN_THREADS, 1)
 attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_vt, AttnParams p) {
@@ -255,7 +257,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         const int row = quarter * 32 + lane;    // query row inside the tile
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         const float c = p.scale * 1.4426950408889634f;  // softmax in the exp2 domain
-        float m_ref = -INFINITY, l_run = 0.0f;
+        float m_ref = FIXED ? p.score_ref : -INFINITY, l_run = 0.0f;
         bool ok = true;
         if (q_prologue) {
             // Prologue: this thread's query row from the raw f32 projection -> per-head RMS norm
@@ -318,6 +320,15 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 if (lane == 0) mbar_arrive(&bars->s_read[t]);
             }
             const int valid = seg_len - j * KT;  // keys of this tile inside the segment
+            if constexpr (FIXED) {
+                if (valid < KT) {
+#pragma unroll
+                    for (int ch = 0; ch < 4; ++ch)
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (ch * 32 + i >= valid) v[ch][i] = 0xff800000u;  // -inf: exp2 gives 0
+                }
+            } else {
             // row maximum: eight independent chains (a single running maximum is a 128-deep
             // dependency chain on the critical path between S and P)
             float mxs[8];
@@ -367,6 +378,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     }
                 }
             }
+            }  // !FIXED
             // exp2(s * c - m) in pairs: packed FMA and packed sums (one issue slot per two elements);
             // POLY_OF_8 of every eight pairs take the polynomial route on the FMA pipe instead of the
             // special-function unit, which is the pipe that bounds this loop
@@ -462,30 +474,39 @@ int attn_smem_bytes(int hd) {
     }
 }
 
-template <int HD, int POLY>
+template <int HD, int POLY, bool FIXED>
 static int launch_hd(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_vt, const AttnParams& p,
                      cudaStream_t stream) {
     static std::atomic<bool> configured[64];  // per instantiation and device; never repeated inside a stream capture
     int dev = 0;
     CMFC_CUDA(cudaGetDevice(&dev));
     if (!configured[dev & 63]) {
-        CMFC_CUDA(cudaFuncSetAttribute(attention_kernel<HD, POLY>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        CMFC_CUDA(cudaFuncSetAttribute(attention_kernel<HD, POLY, FIXED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        AttnSmem<HD>::TOTAL));
         configured[dev & 63] = true;
     }
     dim3 grid((p.max_seg + 2 * QT - 1) / (2 * QT), p.nh, p.nseg);
-    attention_kernel<HD, POLY><<<grid, ATTN_THREADS, AttnSmem<HD>::TOTAL, stream>>>(tm_q, tm_k, tm_vt, p);
+    attention_kernel<HD, POLY, FIXED><<<grid, ATTN_THREADS, AttnSmem<HD>::TOTAL, stream>>>(tm_q, tm_k, tm_vt, p);
     CMFC_CUDA(cudaGetLastError());
     return OK;
 }
 
+template <int HD, int POLY>
+static int launch_ref(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_vt, const AttnParams& p,
+                      cudaStream_t stream) {
+    return p.score_ref > 0.0f ? launch_hd<HD, POLY, true>(tm_q, tm_k, tm_vt, p, stream)
+                              : launch_hd<HD, POLY, false>(tm_q, tm_k, tm_vt, p, stream);
+}
+
 int launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_vt, const AttnParams& p,
                      cudaStream_t stream) {
+    if (p.score_ref < 0.0f || p.score_ref > ATTN_MAX_SCORE_REF)
+        return fail(ERR_BAD_ARG, "attention: the fixed score reference must lie in (0, 48] log2 units, or be 0");
     switch (p.hd) {
-        case 32: return launch_hd<32, 2>(tm_q, tm_k, tm_vt, p, stream);
-        case 64: return launch_hd<64, 2>(tm_q, tm_k, tm_vt, p, stream);
-        case 96: return launch_hd<96, 2>(tm_q, tm_k, tm_vt, p, stream);
-        case 128: return launch_hd<128, 2>(tm_q, tm_k, tm_vt, p, stream);
+        case 32: return launch_ref<32, 2>(tm_q, tm_k, tm_vt, p, stream);
+        case 64: return launch_ref<64, 2>(tm_q, tm_k, tm_vt, p, stream);
+        case 96: return launch_ref<96, 2>(tm_q, tm_k, tm_vt, p, stream);
+        case 128: return launch_ref<128, 2>(tm_q, tm_k, tm_vt, p, stream);
         default: return fail(ERR_UNSUPPORTED, "attention: head_dim must be 32, 64, 96 or 128");
     }
 }

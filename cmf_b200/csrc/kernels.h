@@ -75,7 +75,16 @@ struct AttnParams {
     const float* norm_q = nullptr;
     const float* cos_t = nullptr;
     const float* sin_t = nullptr;
+    // Fixed softmax reference.  When the caller can bound every score of the launch,
+    // max |q_i| * max |k_j| * scale * log2(e) <= score_ref <= ATTN_MAX_SCORE_REF, the kernel uses
+    // score_ref as the reference of every row from the first key tile on: exp2(s - score_ref) can
+    // neither overflow nor, with scores no lower than -score_ref, fall below 2^-96, so the row
+    // maximum and the rescaling of O are not needed at all (softmax is invariant to the reference;
+    // P and the row sum are floating point, so a reference above the true maximum costs no
+    // precision).  0: unknown, the kernel tracks the running row maximum.
+    float score_ref = 0.0f;
 };
+constexpr float ATTN_MAX_SCORE_REF = 48.0f;
 int attn_smem_bytes(int hd);
 int launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_vt,
                      const AttnParams& p, cudaStream_t stream);
@@ -101,6 +110,8 @@ void launch_encode_q4tp(const float* w, int rows, int cols, uint8_t* payload, co
 
 // ---------------- element-wise / row kernels (rowops.cu) ----------------
 void launch_f32_to_bf16(const float* in, __nv_bfloat16* out, size_t n, cudaStream_t s);
+// atomicMax of the squared norms of the bf16 head rows x [heads_total][hd] into *out (float bits; zero it first)
+void launch_head_norm2_max(const __nv_bfloat16* x, size_t heads_total, int hd, unsigned* out, cudaStream_t s);
 void launch_bf16_to_f32(const __nv_bfloat16* in, float* out, size_t n, cudaStream_t s);
 // out_bf16[r, :] = rms(x[r, :]; w, eps) * (1 + shift)   (shift may be null)
 void launch_rms_mod(const float* x, const float* w, const float* shift, double eps, int rows, int cols,

@@ -438,7 +438,35 @@ __global__ void fill_normal_kernel(float* __restrict__ out, size_t n, uint64_t s
     }
 }
 
+// max over heads of the squared Euclidean norm of bf16 head rows [heads_total][hd] (hd % 8 == 0),
+// as the bit pattern of a non-negative float (orders like an unsigned integer)
+__global__ void head_norm2_max_kernel(const __nv_bfloat16* __restrict__ x, size_t heads_total, int hd, unsigned* __restrict__ out) {
+    float best = 0.0f;
+    for (size_t h = blockIdx.x * (size_t)blockDim.x + threadIdx.x; h < heads_total; h += (size_t)gridDim.x * blockDim.x) {
+        const uint4* src = reinterpret_cast<const uint4*>(x + h * hd);
+        float ss = 0.0f;
+        for (int i = 0; i < hd / 8; ++i) {
+            const uint4 w = src[i];
+            const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float a = __uint_as_float(u[k] << 16), b = __uint_as_float(u[k] & 0xffff0000u);
+                ss = fmaf(a, a, fmaf(b, b, ss));
+            }
+        }
+        best = fmaxf(best, ss);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) best = fmaxf(best, __shfl_xor_sync(0xffffffffu, best, o));
+    if ((threadIdx.x & 31) == 0 && best > 0.0f) atomicMax(out, __float_as_uint(best));
+}
+
 }  // namespace
+
+void launch_head_norm2_max(const __nv_bfloat16* x, size_t heads_total, int hd, unsigned* out, cudaStream_t s) {
+    size_t g = (heads_total + 255) / 256;
+    head_norm2_max_kernel<<<(int)(g > 148 * 8 ? 148 * 8 : (g == 0 ? 1 : g)), 256, 0, s>>>(x, heads_total, hd, out);
+}
 
 static inline int grid_for(size_t n, int block) {
     size_t g = (n + block - 1) / block;

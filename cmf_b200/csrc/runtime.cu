@@ -682,8 +682,40 @@ int prepare_segs(Context* c, const std::vector<int>& segs, SegTable* out) {
     return OK;
 }
 
+static bool fixed_ref_enabled() {
+    const char* e = getenv("CMFC_ATTN_FIXED_REF");  // read per call
+    return !(e && e[0] == '0');
+}
+
+float attention_score_ref_from_gain(float qk_gain, int hd) {
+    if (!(qk_gain > 0.0f) || !fixed_ref_enabled()) return 0.0f;
+    // q . k / sqrt(hd) <= |q| |k| / sqrt(hd) <= sqrt(hd) * gain; 2 % covers the f32 arithmetic of the
+    // norm and rotation and the bf16 rounding of both operands
+    const float ref = sqrtf((float)hd) * qk_gain * 1.02f * 1.4426950408889634f;
+    return ref <= ATTN_MAX_SCORE_REF ? ref : 0.0f;
+}
+
+int attention_score_ref(Context* c, const __nv_bfloat16* q, const __nv_bfloat16* k, size_t n_total, int nh, int nkv,
+                        int hd, float scale, float* score_ref) {
+    *score_ref = 0.0f;
+    if (!fixed_ref_enabled() || !(scale > 0.0f)) return OK;
+    DevBuf& b = c->lane_buf("attn_norm2");
+    CMFC_TRY(b.ensure(8));
+    CMFC_CUDA(cudaMemsetAsync(b.p, 0, 8, c->stream));
+    launch_head_norm2_max(q, n_total * nh, hd, b.as<unsigned>(), c->stream);
+    launch_head_norm2_max(k, n_total * nkv, hd, b.as<unsigned>() + 1, c->stream);
+    c->launches += 2;
+    float n2[2];
+    CMFC_CUDA(cudaMemcpyAsync(n2, b.p, 8, cudaMemcpyDeviceToHost, c->stream));
+    CMFC_CUDA(cudaStreamSynchronize(c->stream));
+    const float ref = sqrtf(n2[0]) * sqrtf(n2[1]) * scale * 1.4426950408889634f * 1.001f;
+    if (ref > 0.0f && ref <= ATTN_MAX_SCORE_REF) *score_ref = ref;
+    return OK;
+}
+
 int dev_attention(Context* c, const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* vt,
-                  const SegTable& st, int nh, int nkv, int hd, float scale, __nv_bfloat16* out, const AttnRawQ* raw) {
+                  const SegTable& st, int nh, int nkv, int hd, float scale, __nv_bfloat16* out, const AttnRawQ* raw,
+                  float score_ref) {
     if (hd % 32 || hd > 128 || hd < 32) return fail(ERR_UNSUPPORTED, "attention needs head_dim in {32, 64, 96, 128}");
     if (nh % nkv) return fail(ERR_BAD_ARG, "query heads must be a multiple of kv heads");
     CUtensorMap tm_q, tm_k, tm_vt;
@@ -695,7 +727,7 @@ int dev_attention(Context* c, const __nv_bfloat16* q, const __nv_bfloat16* k, co
     AttnParams p;
     p.nh = nh; p.nkv = nkv; p.hd = hd; p.n_total = st.n_total; p.vt_pitch = st.vt_pitch;
     p.seg_start = st.dev; p.nseg = (int)st.host.size(); p.max_seg = st.max_seg; p.scale = scale;
-    p.out = out; p.status = c->status;
+    p.out = out; p.status = c->status; p.score_ref = score_ref;
     if (raw) {
         if ((reinterpret_cast<uintptr_t>(raw->q_raw) & 15) || raw->ld_q % 4)
             return fail(ERR_BAD_ARG, "attention: the raw query rows must be 16-byte aligned");
@@ -756,8 +788,10 @@ int dev_block(Context* c, const BlockWeights& bw, const BlockMod& mod, float* x,
     {
         SpanGuard g(c, "attention");
         const AttnRawQ raw = {qkv.as<float>(), qkv_w, bw.norm_q, cos_t, sin_t};
+        // the head norm bounds every score, so the softmax reference is known before the launch
         CMFC_TRY(dev_attention(c, qb.as<__nv_bfloat16>(), kb.as<__nv_bfloat16>(), vt.as<__nv_bfloat16>(), st, nh, nkv, hd,
-                               1.0f / sqrtf((float)hd), att.as<__nv_bfloat16>(), q_prologue ? &raw : nullptr));
+                               1.0f / sqrtf((float)hd), att.as<__nv_bfloat16>(), q_prologue ? &raw : nullptr,
+                               attention_score_ref_from_gain(bw.qk_gain, hd)));
     }
     {
         SpanGuard g(c, "o-proj");

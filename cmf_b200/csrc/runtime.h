@@ -150,14 +150,23 @@ struct AttnRawQ {
     int ld_q;
     const float *norm_q, *cos_t, *sin_t;
 };
+// score_ref: AttnParams::score_ref (0: the kernel tracks the row maximum)
 int dev_attention(Context* c, const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* vt,
                   const SegTable& st, int nh, int nkv, int hd, float scale, __nv_bfloat16* out,
-                  const AttnRawQ* raw = nullptr);
+                  const AttnRawQ* raw = nullptr, float score_ref = 0.0f);
+// Measures max |q_i| and max |k_j| over finished bf16 rows on the device (one small launch each and a
+// synchronizing 8-byte read: not for a captured stream) and returns the fixed softmax reference they
+// allow, or 0 when it would exceed ATTN_MAX_SCORE_REF or CMFC_ATTN_FIXED_REF=0 is set.
+int attention_score_ref(Context* c, const __nv_bfloat16* q, const __nv_bfloat16* k, size_t n_total, int nh, int nkv,
+                        int hd, float scale, float* score_ref);
+// the same from the gains of the head norms: rows leave the norm with |q| <= sqrt(hd) * max |w_q|
+float attention_score_ref_from_gain(float qk_gain, int hd);
 
 struct BlockWeights {
     DevWeight *qkv = nullptr, *o = nullptr, *w13 = nullptr, *w2 = nullptr;
     const float *norm1 = nullptr, *norm2 = nullptr, *ffn_norm1 = nullptr, *ffn_norm2 = nullptr;
     const float *norm_q = nullptr, *norm_k = nullptr;
+    float qk_gain = 0.0f;  // max |norm_q| * max |norm_k| (0: unknown, attention tracks the row maximum)
 };
 struct BlockMod {  // all null for an unmodulated block; gates already tanh'd
     const float *s_msa = nullptr, *gate_msa = nullptr, *s_mlp = nullptr, *gate_mlp = nullptr;

@@ -62,3 +62,59 @@ def test_attention_rising_scores_wide_range():
     want = attention_seq(q.reshape(n, -1), k.reshape(n, -1), v.reshape(n, -1), nh, nkv, hd)
     assert np.isfinite(out).all()
     assert rel_l2(out, want) < 6e-3, rel_l2(out, want)
+
+
+def _score_bound_log2(q, k, scale):
+    """max |q_i| * max |k_j| * scale * log2(e): what the entry measures on the device to decide whether the
+    softmax reference can be fixed before the launch (at most 48) or has to follow the running row maximum."""
+    qn = np.sqrt((q.astype(np.float64) ** 2).sum(-1)).max()
+    kn = np.sqrt((k.astype(np.float64) ** 2).sum(-1)).max()
+    return qn * kn * scale * 1.4426950408889634
+
+
+def test_attention_fixed_reference_equals_running_maximum(monkeypatch):
+    """The same bounded input through both softmax forms: reference fixed before the launch (default when
+    the bound allows) and running row maximum (CMFC_ATTN_FIXED_REF=0)."""
+    from cmf_b200 import gpu
+    nh, nkv, hd, n = 6, 2, 96, 900
+    rng = np.random.default_rng(21)
+    q = oc.bf16_round(rng.standard_normal((n, nh, hd)).astype(np.float32))
+    k = oc.bf16_round(rng.standard_normal((n, nkv, hd)).astype(np.float32))
+    v = oc.bf16_round(rng.standard_normal((n, nkv, hd)).astype(np.float32))
+    scale = 1.0 / np.sqrt(hd)
+    assert _score_bound_log2(q, k, scale) < 40
+    outs = []
+    for env in (None, "0"):
+        if env is None:
+            monkeypatch.delenv("CMFC_ATTN_FIXED_REF", raising=False)
+        else:
+            monkeypatch.setenv("CMFC_ATTN_FIXED_REF", env)
+        out = np.empty((n, nh * hd), np.float32)
+        gpu.dit_attention(q.transpose(1, 0, 2), k.transpose(1, 0, 2), v.transpose(1, 0, 2), nh, nkv, n, hd, scale, out)
+        outs.append(out)
+    want = attention_seq(q.reshape(n, -1), k.reshape(n, -1), v.reshape(n, -1), nh, nkv, hd)
+    assert rel_l2(outs[0], want) < 6e-3 and rel_l2(outs[1], want) < 6e-3
+    assert rel_l2(outs[0], outs[1]) < 4e-3
+
+
+def test_attention_fixed_reference_scores_far_below_the_bound():
+    """Every key points away from every query, so all scores of a row sit near MINUS the bound (about 40
+    log2 units): with the reference fixed at plus the bound the exponentials are around 2^-80, still normal
+    numbers, and the result must not lose accuracy."""
+    from cmf_b200 import gpu
+    nh, nkv, hd, n = 2, 2, 64, 300
+    rng = np.random.default_rng(5)
+    u = rng.standard_normal(hd).astype(np.float32)
+    u /= np.linalg.norm(u)
+    q = np.broadcast_to(15.0 * u, (n, nh, hd)).astype(np.float32) + 0.05 * rng.standard_normal((n, nh, hd)).astype(np.float32)
+    k = np.broadcast_to(-14.0 * u, (n, nkv, hd)).astype(np.float32) + 0.3 * rng.standard_normal((n, nkv, hd)).astype(np.float32)
+    q, k = oc.bf16_round(q), oc.bf16_round(k)
+    v = oc.bf16_round(rng.standard_normal((n, nkv, hd)).astype(np.float32))
+    scale = 1.0 / np.sqrt(hd)
+    b = _score_bound_log2(q, k, scale)
+    assert 30 < b < 47, b
+    out = np.empty((n, nh * hd), np.float32)
+    gpu.dit_attention(q.transpose(1, 0, 2), k.transpose(1, 0, 2), v.transpose(1, 0, 2), nh, nkv, n, hd, scale, out)
+    want = attention_seq(q.reshape(n, -1), k.reshape(n, -1), v.reshape(n, -1), nh, nkv, hd)
+    assert np.isfinite(out).all()
+    assert rel_l2(out, want) < 6e-3, rel_l2(out, want)
