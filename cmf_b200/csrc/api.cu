@@ -208,6 +208,10 @@ extern "C" int cmfc_dit_attention(const float* qh, const float* kh, const float*
     c->launches += 3;
     float score_ref = 0.0f;
     CMFC_TRY(attention_score_ref(c, qb.as<__nv_bfloat16>(), kb.as<__nv_bfloat16>(), n, (int)nh, (int)nkv, (int)hd, scale, &score_ref));
+    if (score_ref > 0.0f) {  // the bounded form takes its queries multiplied by scale * log2(e)
+        launch_transpose_head_major(d_in, (int)nh, (int)n, (int)hd, scale * 1.4426950408889634f, qb.as<__nv_bfloat16>(), c->stream);
+        c->launches++;
+    }
     CMFC_TRY(dev_attention(c, qb.as<__nv_bfloat16>(), kb.as<__nv_bfloat16>(), vt.as<__nv_bfloat16>(), st, (int)nh, (int)nkv,
                            (int)hd, scale, ob.as<__nv_bfloat16>(), nullptr, score_ref));
     launch_bf16_to_f32(ob.as<__nv_bfloat16>(), of.as<float>(), qn, c->stream);
@@ -1178,6 +1182,11 @@ extern "C" int cmfc_bench_attention(size_t nh, size_t nkv, size_t hd, size_t n, 
     const float scale = 1.0f / sqrtf((float)hd);
     float score_ref = 0.0f;  // the form a NextDiT block launches: the reference known in advance
     CMFC_TRY(attention_score_ref(c, q.as<__nv_bfloat16>(), k.as<__nv_bfloat16>(), tot, (int)nh, (int)nkv, (int)hd, scale, &score_ref));
+    if (score_ref > 0.0f) {  // same queries, multiplied by scale * log2(e)
+        launch_fill_normal(f.as<float>(), qn, 11, scale * 1.4426950408889634f, c->stream);
+        launch_f32_to_bf16(f.as<float>(), q.as<__nv_bfloat16>(), qn, c->stream);
+        c->launches += 2;
+    }
     for (int i = 0; i < 3; ++i)
         CMFC_TRY(dev_attention(c, q.as<__nv_bfloat16>(), k.as<__nv_bfloat16>(), v.as<__nv_bfloat16>(), st, (int)nh, (int)nkv, (int)hd, scale, o.as<__nv_bfloat16>(), nullptr, score_ref));
     cudaEvent_t e0, e1;
@@ -1222,7 +1231,7 @@ extern "C" int cmfc_bench_rowop(int kind, size_t rows, size_t cols, int iters, f
         if (kind == 0) launch_rms_mod(x.as<float>(), v0, v0 + cols, 1e-5, (int)rows, (int)cols, ob.as<__nv_bfloat16>(), nullptr, c->stream);
         else if (kind == 1) launch_gated_residual(x.as<float>(), src.as<float>(), v0, v0 + cols, 1e-5, (int)rows, (int)cols, c->stream);
         else if (kind == 2) launch_residual_then_norm(x.as<float>(), src.as<float>(), v0, v0 + cols, v0 + 2 * cols, v0 + 3 * cols, 1e-5, (int)rows, (int)cols, ob.as<__nv_bfloat16>(), c->stream);
-        else launch_qk_rope_pack(x.as<float>(), (int)rows, nh, nkv, hd, v0, v0 + hd, tab.as<float>(), tab.as<float>() + rows * hd / 2, ob.as<__nv_bfloat16>(), o2.as<__nv_bfloat16>(), c->stream);
+        else launch_qk_rope_pack(x.as<float>(), (int)rows, nh, nkv, hd, v0, v0 + hd, tab.as<float>(), tab.as<float>() + rows * hd / 2, 1.0f, ob.as<__nv_bfloat16>(), o2.as<__nv_bfloat16>(), c->stream);
         c->launches++;
     };
     for (int i = 0; i < 3; ++i) run();

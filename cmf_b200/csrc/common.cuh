@@ -254,6 +254,14 @@ __device__ __forceinline__ void tmem_ld_x32(uint32_t taddr, uint32_t (&r)[32]) {
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
 __device__ __forceinline__ void tmem_ld_x8(uint32_t taddr, uint32_t (&r)[8]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
@@ -331,9 +339,11 @@ __device__ __forceinline__ float max3_f32(float a, float b, float c) {
 // 2^t for a pair without the special-function unit: n = round(t) through the 1.5 * 2^23 trick,
 // a cubic for 2^(t - n) on [-0.5, 0.5] (relative error 7.5e-5, far below the bf16 rounding the
 // result gets), n added into the exponent field.  t is clamped at -126.
+// CLAMP = false: the caller guarantees t >= -126.
+template <bool CLAMP = true>
 __device__ __forceinline__ void ex2_poly_x2(float t0, float t1, float& e0, float& e1) {
     const float MAGIC = 12582912.0f;
-    const uint64_t t = pack_f32x2(fmaxf(t0, -126.0f), fmaxf(t1, -126.0f));
+    const uint64_t t = CLAMP ? pack_f32x2(fmaxf(t0, -126.0f), fmaxf(t1, -126.0f)) : pack_f32x2(t0, t1);
     const uint64_t r = add_f32x2(t, pack_f32x2(MAGIC, MAGIC));
     const uint64_t n = add_f32x2(r, pack_f32x2(-MAGIC, -MAGIC));
     const uint64_t f = fma_f32x2(n, pack_f32x2(-1.0f, -1.0f), t);
@@ -344,8 +354,9 @@ __device__ __forceinline__ void ex2_poly_x2(float t0, float t1, float& e0, float
     float r0, r1, q0, q1;
     unpack_f32x2(r, r0, r1);
     unpack_f32x2(q, q0, q1);
-    e0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(r0) << 23));
-    e1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(r1) << 23));
+    // exponent insertion as one integer multiply-add: q + (r << 23)
+    e0 = __uint_as_float(__float_as_uint(r0) * 0x800000u + __float_as_uint(q0));
+    e1 = __uint_as_float(__float_as_uint(r1) * 0x800000u + __float_as_uint(q1));
 }
 
 // Row statistics: the squares of four neighbouring values are summed in f32 (relative error

@@ -75,17 +75,18 @@ struct AttnParams {
     const float* norm_q = nullptr;
     const float* cos_t = nullptr;
     const float* sin_t = nullptr;
-    // Fixed softmax reference.  When the caller can bound every score of the launch,
-    // max |q_i| * max |k_j| * scale * log2(e) <= score_ref <= ATTN_MAX_SCORE_REF, the kernel uses
-    // score_ref as the reference of every row from the first key tile on: exp2(s - score_ref) can
-    // neither overflow nor, with scores no lower than -score_ref, fall below 2^-96, so the row
-    // maximum and the rescaling of O are not needed at all (softmax is invariant to the reference;
-    // P and the row sum are floating point, so a reference above the true maximum costs no
-    // precision).  0: unknown, the kernel tracks the running row maximum.
+    // Bounded form (score_ref > 0).  The caller guarantees two things: the query rows are already
+    // multiplied by scale * log2(e) (`scale` is then ignored), and every score of the launch lies
+    // within +-score_ref, max |q_i| * max |k_j| <= score_ref <= ATTN_MAX_SCORE_REF.  The kernel then
+    // takes P = exp2(S) straight from the MMA result: between 2^-48 and 2^48 nothing overflows or
+    // vanishes in f32 / bf16, softmax does not depend on the reference, and P and the row sum are
+    // floating point, so no row maximum, no subtraction and no rescaling of O are needed.
+    // 0: unknown bound; the kernel scales the scores itself and tracks the running row maximum.
     float score_ref = 0.0f;
 };
 constexpr float ATTN_MAX_SCORE_REF = 48.0f;
 int attn_smem_bytes(int hd);
+int attn_key_tile(int hd);  // keys per K tile: the row count of the K tensor map's box
 int launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_vt,
                      const AttnParams& p, cudaStream_t stream);
 
@@ -126,8 +127,9 @@ void launch_residual_then_norm(float* x, const float* src, const float* w_res, c
 // per (token, head): qk RMS norm (eps 1e-5) + interleaved-pair RoPE (cos / sin [n, hd/2] f32); writes Q, K bf16
 // token-major (V never passes through here: the QKV GEMM's epilogue writes V^T itself)
 // q == nullptr: only the K heads (the attention kernel then normalises and rotates Q in its prologue)
+// q_scale multiplies the finished query rows (1, or scale * log2(e) for the bounded attention form)
 void launch_qk_rope_pack(const float* qkv, int n, int nh, int nkv, int hd, const float* norm_q,
-                         const float* norm_k, const float* cos_t, const float* sin_t, __nv_bfloat16* q,
+                         const float* norm_k, const float* cos_t, const float* sin_t, float q_scale, __nv_bfloat16* q,
                          __nv_bfloat16* k, cudaStream_t s);
 // y[r] = act_out( dot(W[r, :], act_in(x)) * scale[r] + b[r] ); W f32 or int8 (+row scales)
 // act_in: 0 none, 1 silu.  tanh_lo..tanh_hi: rows in [lo0,hi0) or [lo1,hi1) get tanh.

@@ -183,7 +183,7 @@ template <int PPL>  // hd / 32
 __global__ void __launch_bounds__(ROPE_THREADS, PPL <= 3 ? 8 : 4)
 qk_rope_kernel(const float* __restrict__ qkv, int n, int nh, int nkv, const float* __restrict__ norm_q,
                const float* __restrict__ norm_k, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
-               __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_out) {
+               float q_scale, __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_out) {
     constexpr int hd = 32 * PPL;
     const int h_first = q_out ? 0 : nh;  // without a Q output only the K heads are walked
     const int heads = nh + nkv - h_first;
@@ -211,6 +211,7 @@ qk_rope_kernel(const float* __restrict__ qkv, int n, int nh, int nkv, const floa
     ss += __shfl_xor_sync(0xffffffffu, ss, 1);
     const float inv = (float)(1.0 / sqrt(ss / hd + 1e-5));
     if (!active) return;
+    const float os = is_q ? q_scale : 1.0f;
     __nv_bfloat16* dst = (is_q ? q_out + (size_t)tok * nh * hd + (size_t)h * hd
                                : k_out + (size_t)tok * nkv * hd + (size_t)(h - nh) * hd) + l * 8;
 #pragma unroll
@@ -219,7 +220,7 @@ qk_rope_kernel(const float* __restrict__ qkv, int n, int nh, int nkv, const floa
         const float4 cs = ld4(ct + g * 16), sn = ld4(st + g * 16);
         auto rot = [&](float x, float y, float gx, float gy, float c, float s_) {
             const float a = rms_elem(x, inv, gx), b = rms_elem(y, inv, gy);
-            return pack_bf16(fmaf(a, c, -(b * s_)), fmaf(a, s_, b * c));
+            return pack_bf16(fmaf(a, c, -(b * s_)) * os, fmaf(a, s_, b * c) * os);
         };
         uint4 o;
         o.x = rot(v[g][0].x, v[g][0].y, g0.x, g0.y, cs.x, sn.x);
@@ -513,15 +514,15 @@ bool row_cols_supported(int cols) {
 }
 
 void launch_qk_rope_pack(const float* qkv, int n, int nh, int nkv, int hd, const float* norm_q,
-                         const float* norm_k, const float* cos_t, const float* sin_t, __nv_bfloat16* q,
+                         const float* norm_k, const float* cos_t, const float* sin_t, float q_scale, __nv_bfloat16* q,
                          __nv_bfloat16* k, cudaStream_t s) {
     const long items = (long)n * ((q ? nh : 0) + nkv);
     const int grid = (int)((items + ROPE_THREADS / 4 - 1) / (ROPE_THREADS / 4));
     switch (hd / 32) {
-        case 1: qk_rope_kernel<1><<<grid, ROPE_THREADS, 0, s>>>(qkv, n, nh, nkv, norm_q, norm_k, cos_t, sin_t, q, k); break;
-        case 2: qk_rope_kernel<2><<<grid, ROPE_THREADS, 0, s>>>(qkv, n, nh, nkv, norm_q, norm_k, cos_t, sin_t, q, k); break;
-        case 3: qk_rope_kernel<3><<<grid, ROPE_THREADS, 0, s>>>(qkv, n, nh, nkv, norm_q, norm_k, cos_t, sin_t, q, k); break;
-        case 4: qk_rope_kernel<4><<<grid, ROPE_THREADS, 0, s>>>(qkv, n, nh, nkv, norm_q, norm_k, cos_t, sin_t, q, k); break;
+        case 1: qk_rope_kernel<1><<<grid, ROPE_THREADS, 0, s>>>(qkv, n, nh, nkv, norm_q, norm_k, cos_t, sin_t, q_scale, q, k); break;
+        case 2: qk_rope_kernel<2><<<grid, ROPE_THREADS, 0, s>>>(qkv, n, nh, nkv, norm_q, norm_k, cos_t, sin_t, q_scale, q, k); break;
+        case 3: qk_rope_kernel<3><<<grid, ROPE_THREADS, 0, s>>>(qkv, n, nh, nkv, norm_q, norm_k, cos_t, sin_t, q_scale, q, k); break;
+        case 4: qk_rope_kernel<4><<<grid, ROPE_THREADS, 0, s>>>(qkv, n, nh, nkv, norm_q, norm_k, cos_t, sin_t, q_scale, q, k); break;
         default: break;
     }
 }

@@ -719,9 +719,9 @@ int dev_attention(Context* c, const __nv_bfloat16* q, const __nv_bfloat16* k, co
     if (hd % 32 || hd > 128 || hd < 32) return fail(ERR_UNSUPPORTED, "attention needs head_dim in {32, 64, 96, 128}");
     if (nh % nkv) return fail(ERR_BAD_ARG, "query heads must be a multiple of kv heads");
     CUtensorMap tm_q, tm_k, tm_vt;
-    // Q / K: [n_total, heads*hd] bf16, boxes of 128 tokens x 32 dims, 64-byte swizzle
+    // Q / K: [n_total, heads*hd] bf16, boxes of 128 queries / one key tile x 32 dims, 64-byte swizzle
     CMFC_TRY(make_tensor_map_2d(&tm_q, q, 2, st.n_total, (uint64_t)nh * hd, (uint64_t)nh * hd * 2, 128, 32, 2));
-    CMFC_TRY(make_tensor_map_2d(&tm_k, k, 2, st.n_total, (uint64_t)nkv * hd, (uint64_t)nkv * hd * 2, 128, 32, 2));
+    CMFC_TRY(make_tensor_map_2d(&tm_k, k, 2, st.n_total, (uint64_t)nkv * hd, (uint64_t)nkv * hd * 2, attn_key_tile(hd), 32, 2));
     // V^T: [nkv*hd, vt_pitch] bf16, boxes of hd rows x 64 keys, 128-byte swizzle
     CMFC_TRY(make_tensor_map_2d(&tm_vt, vt, 2, (uint64_t)nkv * hd, (uint64_t)st.vt_pitch, (uint64_t)st.vt_pitch * 2, hd, 64, 3));
     AttnParams p;
@@ -779,19 +779,22 @@ int dev_block(Context* c, const BlockWeights& bw, const BlockMod& mod, float* x,
     // separate pass is the default.
     const char* pro_env = getenv("CMFC_ROPE_PROLOGUE");  // read per call
     const bool q_prologue = pro_env && pro_env[0] == '1';
+    // the head norm bounds every score, so attention can take the bounded form (AttnParams::score_ref),
+    // whose queries come multiplied by scale * log2(e)
+    const float attn_scale = 1.0f / sqrtf((float)hd);
+    const float score_ref = attention_score_ref_from_gain(bw.qk_gain, hd);
     {
         SpanGuard g(c, "rope");
         launch_qk_rope_pack(qkv.as<float>(), n, nh, nkv, hd, bw.norm_q, bw.norm_k, cos_t, sin_t,
+                            score_ref > 0.0f ? attn_scale * 1.4426950408889634f : 1.0f,
                             q_prologue ? nullptr : qb.as<__nv_bfloat16>(), kb.as<__nv_bfloat16>(), s);
         c->launches++;
     }
     {
         SpanGuard g(c, "attention");
         const AttnRawQ raw = {qkv.as<float>(), qkv_w, bw.norm_q, cos_t, sin_t};
-        // the head norm bounds every score, so the softmax reference is known before the launch
         CMFC_TRY(dev_attention(c, qb.as<__nv_bfloat16>(), kb.as<__nv_bfloat16>(), vt.as<__nv_bfloat16>(), st, nh, nkv, hd,
-                               1.0f / sqrtf((float)hd), att.as<__nv_bfloat16>(), q_prologue ? &raw : nullptr,
-                               attention_score_ref_from_gain(bw.qk_gain, hd)));
+                               attn_scale, att.as<__nv_bfloat16>(), q_prologue ? &raw : nullptr, score_ref));
     }
     {
         SpanGuard g(c, "o-proj");
