@@ -97,7 +97,7 @@ struct AttnSmem {
 
 // POLY_OF_8: pairs out of every eight whose exp2 runs on the FMA pipe instead of the special-function unit.
 // FIXED: the queries arrive multiplied by scale * log2(e) and every score of the launch is known to lie
-// within +-p.score_ref <= 48 (see AttnParams): P = exp2(S) as it comes out of the MMA -- no scaling, no
+// within +-p.score_ref <= 96 (see AttnParams): P = exp2(S) as it comes out of the MMA -- no scaling, no
 // reference, no row maximum, no rescaling of O.
 template <int HD, int POLY_OF_8, bool FIXED>
 __global__ void __launch_bounds__((attn_threads<HD, FIXED>()), 1)
@@ -113,10 +113,6 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     constexpr int NCH = COLS / CW;                     // chunks of a thread's scores
     constexpr int MMA_B_WARP = 2 + 2 * WPT;
     static_assert(FIXED || HALVES == 1, "the running row maximum needs the whole row in one thread");
-#ifndef CMFC_ATTN_TURN_CH
-#define CMFC_ATTN_TURN_CH (NCH - 1)
-#endif
-    constexpr int TURN_CH = CMFC_ATTN_TURN_CH;  // the other tile may start its exponentials after this chunk
     const int seg = blockIdx.z, head = blockIdx.y;
     const int seg0 = p.seg_start[seg];
     const int seg_len = p.seg_start[seg + 1] - seg0;
@@ -368,7 +364,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     for (int ch = 0; ch < NCH; ++ch)
 #pragma unroll
                         for (int i = 0; i < CW; ++i)
-                            if (half * COLS + ch * CW + i >= valid) v[ch][i] = 0xc2fc0000u;  // -126: 2^-126 beside P >= 2^-48
+                            if (half * COLS + ch * CW + i >= valid) v[ch][i] = 0xc2fc0000u;  // -126: 2^-126 beside P >= 2^-96
                 }
             } else if constexpr (HALVES == 1) {
             // row maximum: eight independent chains (a single running maximum is a 128-deep
@@ -431,11 +427,41 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 // next S and its TMEM load hide behind the other tile's exponentials.  (With the row
                 // maximum tracked in the kernel the turns measured slower than running free.)
                 if (t == 1 || j > 0) {
-                    if (!mbar_wait<40>(&bars->turn[t ^ 1], (t == 1 ? j : j - 1) & 1u, abort_flag, 25)) { ok = false; break; }
+                    if (!mbar_wait(&bars->turn[t ^ 1], (t == 1 ? j : j - 1) & 1u, abort_flag, 25)) { ok = false; break; }
                 }
             }
             uint64_t sums[4] = {0ull, 0ull, 0ull, 0ull};
             uint32_t pk[NCH][CW / 2];
+            if constexpr (split_plan<HD>() && FIXED) {
+                // Inside the turn only what needs the special-function unit (and the polynomial route
+                // that relieves it): the exponentials replace the scores in place.  Packing to bf16 and
+                // the row sum follow after the turn is handed over, beside the other tile's exponentials.
+#pragma unroll
+                for (int ch = 0; ch < NCH; ++ch)
+#pragma unroll
+                    for (int i = 0; i < CW; i += 2) {
+                        const float t0 = __uint_as_float(v[ch][i]), t1 = __uint_as_float(v[ch][i + 1]);
+                        float e0, e1;
+                        if (((i >> 1) & 7) < POLY_OF_8) {
+                            ex2_poly_x2<false>(t0, t1, e0, e1);
+                        } else {
+                            e0 = ex2_approx(t0);
+                            e1 = ex2_approx(t1);
+                        }
+                        v[ch][i] = __float_as_uint(e0);
+                        v[ch][i + 1] = __float_as_uint(e1);
+                    }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars->turn[t]);
+#pragma unroll
+                for (int ch = 0; ch < NCH; ++ch)
+#pragma unroll
+                    for (int i = 0; i < CW; i += 2) {
+                        const float e0 = __uint_as_float(v[ch][i]), e1 = __uint_as_float(v[ch][i + 1]);
+                        sums[(i >> 1) & 3] = add_f32x2(sums[(i >> 1) & 3], pack_f32x2(e0, e1));
+                        pk[ch][i >> 1] = pack_bf16(e0, e1);
+                    }
+            } else {
             const uint64_t c2 = pack_f32x2(c, c), nm2 = pack_f32x2(-m_ref, -m_ref);
 #pragma unroll
             for (int ch = 0; ch < NCH; ++ch) {
@@ -457,16 +483,14 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     sums[(i >> 1) & 3] = add_f32x2(sums[(i >> 1) & 3], pack_f32x2(e0, e1));
                     pk[ch][i >> 1] = pack_bf16(e0, e1);
                 }
-                if constexpr (!split_plan<HD>()) tmem_st_x16(tmem + lane_addr + p_col<HD>(t) + ch * 16, pk[ch]);
-                if constexpr (split_plan<HD>() && FIXED) {
-                    if (ch == TURN_CH) {
+                if constexpr (!split_plan<HD>()) {
+                    tmem_st_x16(tmem + lane_addr + p_col<HD>(t) + ch * 16, pk[ch]);
+                    if (ch == 1 && t == 0 && j == 0) {
                         __syncwarp();
-                        if (lane == 0) mbar_arrive(&bars->turn[t]);
+                        if (lane == 0) mbar_arrive(&bars->stagger);
                     }
-                } else if (!split_plan<HD>() && ch == 1 && t == 0 && j == 0) {
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&bars->stagger);
                 }
+            }
             }
             if constexpr (split_plan<HD>()) {
                 // The tile's own P buffer is free once P V of its previous key tile has run, which was
@@ -575,7 +599,7 @@ static int launch_ref(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CU
 int launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_vt, const AttnParams& p,
                      cudaStream_t stream) {
     if (p.score_ref < 0.0f || p.score_ref > ATTN_MAX_SCORE_REF)
-        return fail(ERR_BAD_ARG, "attention: the fixed score reference must lie in (0, 48] log2 units, or be 0");
+        return fail(ERR_BAD_ARG, "attention: the score bound must lie in (0, 96] log2 units, or be 0");
     switch (p.hd) {
         case 32: return launch_ref<32, 3>(tm_q, tm_k, tm_vt, p, stream);
         case 64: return launch_ref<64, 3>(tm_q, tm_k, tm_vt, p, stream);

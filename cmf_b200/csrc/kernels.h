@@ -78,13 +78,14 @@ struct AttnParams {
     // Bounded form (score_ref > 0).  The caller guarantees two things: the query rows are already
     // multiplied by scale * log2(e) (`scale` is then ignored), and every score of the launch lies
     // within +-score_ref, max |q_i| * max |k_j| <= score_ref <= ATTN_MAX_SCORE_REF.  The kernel then
-    // takes P = exp2(S) straight from the MMA result: between 2^-48 and 2^48 nothing overflows or
-    // vanishes in f32 / bf16, softmax does not depend on the reference, and P and the row sum are
-    // floating point, so no row maximum, no subtraction and no rescaling of O are needed.
+    // takes P = exp2(S) straight from the MMA result: between 2^-96 and 2^96 nothing overflows or
+    // vanishes in f32 / bf16 (a row sum stays below 2^96 times the key count, O below that times
+    // |v|), softmax does not depend on the reference, and P and the row sum are floating point, so no
+    // row maximum, no subtraction and no rescaling of O are needed.
     // 0: unknown bound; the kernel scales the scores itself and tracks the running row maximum.
     float score_ref = 0.0f;
 };
-constexpr float ATTN_MAX_SCORE_REF = 48.0f;
+constexpr float ATTN_MAX_SCORE_REF = 96.0f;
 int attn_smem_bytes(int hd);
 int attn_key_tile(int hd);  // keys per K tile: the row count of the K tensor map's box
 int launch_attention(const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_vt,

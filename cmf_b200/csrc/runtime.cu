@@ -1,5 +1,7 @@
 // Host runtime: errors, device contexts, the memory-mapped container reader, weight upload
 // into kernel planes, and the device-level block composed from the kernels.
+#include <algorithm>
+
 #include "runtime.h"
 
 #include <fcntl.h>
@@ -651,8 +653,15 @@ int dev_gemm(Context* c, DevWeight* w, const __nv_bfloat16* x, int M, void* out,
 // segment (8-aligned, so every TMA x coordinate is a multiple of 16 bytes).  Re-uploaded only
 // when the segmentation changes.
 int prepare_segs(Context* c, const std::vector<int>& segs, SegTable* out) {
-    for (auto& e : c->seg_cache)
-        if (e.first.host == segs) { *out = e.first; return OK; }
+    for (size_t i = 0; i < c->seg_cache.size(); ++i)
+        if (c->seg_cache[i].first.host == segs) {
+            // most recently used last: an entry a forward has just used is never the one a later miss
+            // of the same forward evicts (a captured step must find every table its warm-up step made)
+            if (i + 1 != c->seg_cache.size())
+                std::rotate(c->seg_cache.begin() + i, c->seg_cache.begin() + i + 1, c->seg_cache.end());
+            *out = c->seg_cache.back().first;
+            return OK;
+        }
     std::vector<int> tab(2 * segs.size() + 1, 0);
     int mx = 0, col = 0;
     for (size_t i = 0; i < segs.size(); ++i) {
@@ -662,7 +671,7 @@ int prepare_segs(Context* c, const std::vector<int>& segs, SegTable* out) {
         col += (segs[i] + 7) & ~7;
         mx = segs[i] > mx ? segs[i] : mx;
     }
-    if (c->seg_cache.size() >= 16) {  // a forward alternates between a handful of segmentations
+    if (c->seg_cache.size() >= 32) {  // a forward alternates between a handful of segmentations; the least recently used goes
         CMFC_CUDA(cudaStreamSynchronize(c->main_stream));  // queued kernels of either chain may still read the table
         CMFC_CUDA(cudaStreamSynchronize(c->side_stream));
         c->seg_cache.front().second.release();

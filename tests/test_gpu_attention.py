@@ -65,16 +65,17 @@ def test_attention_rising_scores_wide_range():
 
 
 def _score_bound_log2(q, k, scale):
-    """max |q_i| * max |k_j| * scale * log2(e): what the entry measures on the device to decide whether the
-    softmax reference can be fixed before the launch (at most 48) or has to follow the running row maximum."""
+    """max |q_i| * max |k_j| * scale * log2(e): what the entry measures on the device to decide between the
+    bounded form (at most 96: P = exp2 of the pre-scaled score, no reference at all) and the form that
+    follows the running row maximum."""
     qn = np.sqrt((q.astype(np.float64) ** 2).sum(-1)).max()
     kn = np.sqrt((k.astype(np.float64) ** 2).sum(-1)).max()
     return qn * kn * scale * 1.4426950408889634
 
 
-def test_attention_fixed_reference_equals_running_maximum(monkeypatch):
-    """The same bounded input through both softmax forms: reference fixed before the launch (default when
-    the bound allows) and running row maximum (CMFC_ATTN_FIXED_REF=0)."""
+def test_attention_bounded_form_equals_running_maximum(monkeypatch):
+    """The same bounded input through both softmax forms: the bounded one (default when the bound allows)
+    and the running row maximum (CMFC_ATTN_FIXED_REF=0)."""
     from cmf_b200 import gpu
     nh, nkv, hd, n = 6, 2, 96, 900
     rng = np.random.default_rng(21)
@@ -97,22 +98,23 @@ def test_attention_fixed_reference_equals_running_maximum(monkeypatch):
     assert rel_l2(outs[0], outs[1]) < 4e-3
 
 
-def test_attention_fixed_reference_scores_far_below_the_bound():
-    """Every key points away from every query, so all scores of a row sit near MINUS the bound (about 40
-    log2 units): with the reference fixed at plus the bound the exponentials are around 2^-80, still normal
-    numbers, and the result must not lose accuracy."""
+@pytest.mark.parametrize("sign,qa,ka,lo,hi", [(-1.0, 15.0, 14.0, 30, 47), (-1.0, 22.0, 21.0, 75, 95), (1.0, 22.0, 21.0, 75, 95)])
+def test_attention_bounded_form_scores_at_the_edge_of_the_bound(sign, qa, ka, lo, hi):
+    """Every key points away from (or along) every query, so all scores of a row sit near minus (plus) the
+    bound: the exponentials are around 2^-85 (2^85), still normal numbers in f32 and bf16, and the result
+    must not lose accuracy."""
     from cmf_b200 import gpu
     nh, nkv, hd, n = 2, 2, 64, 300
     rng = np.random.default_rng(5)
     u = rng.standard_normal(hd).astype(np.float32)
     u /= np.linalg.norm(u)
-    q = np.broadcast_to(15.0 * u, (n, nh, hd)).astype(np.float32) + 0.05 * rng.standard_normal((n, nh, hd)).astype(np.float32)
-    k = np.broadcast_to(-14.0 * u, (n, nkv, hd)).astype(np.float32) + 0.3 * rng.standard_normal((n, nkv, hd)).astype(np.float32)
+    q = np.broadcast_to(qa * u, (n, nh, hd)).astype(np.float32) + 0.05 * rng.standard_normal((n, nh, hd)).astype(np.float32)
+    k = np.broadcast_to(sign * ka * u, (n, nkv, hd)).astype(np.float32) + 0.3 * rng.standard_normal((n, nkv, hd)).astype(np.float32)
     q, k = oc.bf16_round(q), oc.bf16_round(k)
     v = oc.bf16_round(rng.standard_normal((n, nkv, hd)).astype(np.float32))
     scale = 1.0 / np.sqrt(hd)
     b = _score_bound_log2(q, k, scale)
-    assert 30 < b < 47, b
+    assert lo < b < hi, b
     out = np.empty((n, nh * hd), np.float32)
     gpu.dit_attention(q.transpose(1, 0, 2), k.transpose(1, 0, 2), v.transpose(1, 0, 2), nh, nkv, n, hd, scale, out)
     want = attention_seq(q.reshape(n, -1), k.reshape(n, -1), v.reshape(n, -1), nh, nkv, hd)

@@ -201,3 +201,28 @@ def test_lumina_geometry_two_layers(tmp_path):
     for l, want in enumerate(joint):
         assert rel_l2(taps[l], want) < TOL, (l, rel_l2(taps[l], want))
     assert rel_l2(pc, oc_) < TOL and rel_l2(pu, ou_) < TOL
+
+
+def test_captured_step_after_many_segmentations(tmp_path):
+    """The device copies of the segment tables are cached per segmentation, least recently used first
+    out.  Forty different attention shapes fill and turn over that cache; the denoise loop that
+    follows (a warm-up step, then captured steps that may not upload anything) must still find every
+    table its warm-up step used."""
+    from cmf_b200 import GenParams, Model, NextDit, denoise, gpu
+    rng = np.random.default_rng(2)
+    for n in range(130, 170):
+        q = rng.standard_normal((2, n, 64)).astype(np.float32)
+        out = np.empty((n, 128), np.float32)
+        gpu.dit_attention(q, q, q, 2, 2, n, 64, 0.125, out)
+    cfg = synth.TINY
+    path = str(tmp_path / "m.cmf")
+    tensors, _ = build(cfg, path, synth.quant_plan(cfg, oc.Q8_ROW, oc.Q8_ROW), seed=1)
+    lat = nd.gauss_latent(16 * 16 * 16, 0).reshape(1, 16, 16, 16)
+    cap = rng.standard_normal((1, 12, 256)).astype(np.float32)
+    cap_u = rng.standard_normal((1, 5, 256)).astype(np.float32)
+    with Model(path) as m:
+        dit = NextDit(m)
+        got = denoise(dit, lat, cap, cap_u, GenParams(steps=3, guidance_scale=4.0))
+        dit.close()
+    want = nd.denoise(nd.NextDitOracle(tensors, cfg), lat[0], 16, 16, cap[0], cap_u[0], steps=3, gs=4.0)
+    assert rel_l2(got[0], want) < TOL
