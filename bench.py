@@ -15,7 +15,8 @@ device-side encoder, which is byte-identical to the reference quantizer).
 Beside the headline the line carries `fixed_batch`: a FIXED batch of 8 prompts (q4tp feed-forward +
 q8 attention weights, seeds 0..7) split over the N GPUs with one gather of the final latents, so
 that the ratio of its `value` between N = 1 and N = 8 is the strong-scaling factor of the batched
-CFG workload; with two or more GPUs also `fixed_batch_2048` (16 prompts at 2048x2048, q4_tiled).
+CFG workload; with two or more GPUs also `fixed_batch_2048` (16 prompts at 2048x2048, q4_tiled); on one
+GPU also `q8_30_steps` (q8_row weights, one prompt, the whole 30-step loop through the public call).
 
 Prints ONE JSON line on rank 0.
 """
@@ -562,10 +563,37 @@ def main():
             own_model.close()
         return res
 
+    def full_loop_leg(codec, steps):
+        """One prompt, CFG pair, the whole Euler loop of `steps` steps through cmf_b200.denoise with pinned host
+        buffers in and out (q8_row weights on every projection: the largest weight footprint of the three codecs)."""
+        res = {"workload": f"lumina2-2.6B {codec} NextDiT, {8 * H}x{8 * H}, 1 prompt x CFG pair, {steps} Euler steps, 1 GPU",
+               "steps": steps, "unit": UNIT}
+        try:
+            m8, d8 = open_model(codec)
+            f_l, f_c, f_u = prompt_inputs([0], H, cfg["cap_feat"], 0)
+            gp = GenParams(steps=steps, guidance_scale=4.0)
+            denoise(d8, f_l, f_c, f_u, GenParams(steps=2, guidance_scale=4.0))   # warm-up: upload, workspaces, capture
+            torch.cuda.synchronize()
+            t0 = time.time()
+            out = denoise(d8, f_l, f_c, f_u, gp)
+            torch.cuda.synchronize()
+            dt = time.time() - t0
+            res.update({"value": steps / dt, "ms_per_step": dt / steps * 1e3, "loops_per_s": 1.0 / dt,
+                        "finite": bool(np.isfinite(out).all()),
+                        "timed": "wall clock around the public call, host buffers in and out, loop set-up (caption "
+                                 "refiner, RoPE tables, graph capture) included"})
+            d8.close()
+            m8.close()
+        except Exception as e:  # noqa: BLE001  (a secondary figure: never hide the headline line)
+            res["failed"] = repr(e)
+        return res
+
     if not args.no_fixed_batch:
         fb = fixed_batch_leg("q4tp_ffn_q8_attn", H, args.fixed_prompts, args.fixed_steps)
         if rank == 0:
             line["fixed_batch"] = fb
+        if world == 1 and args.codec == "q4t":
+            line["q8_30_steps"] = full_loop_leg("q8", 30)
         if world > 1 and args.codec == "q4t":
             fb2 = fixed_batch_leg("q4t", 256, 16, 2, d=dit)
             if rank == 0:
