@@ -4,7 +4,7 @@ library).  Used for the per-kernel roofline tables and as the small cases for pr
     python -m cmf_b200.microbench gemm --codec q4t --N 2304 --K 2304 --M 8704
     python -m cmf_b200.microbench attention --n 4352 --nseg 2
     python -m cmf_b200.microbench rowops --rows 8704
-    python -m cmf_b200.microbench sweep          # the op-level dequant-GEMM sweep of the baseline config
+    python -m cmf_b200.microbench sweep          # dequant GEMM over (K, N) x M x codec: 4 Lumina-2 projection shapes, M = 256 / 4352 / 17408
     python -m cmf_b200.microbench conv --ic 128 --oc 128 --h 1024 --w 1024
     python -m cmf_b200.microbench vae --latent 128   # whole FLUX-VAE decode with per-stage times
     python -m cmf_b200.microbench gemma --n 128 --codec q4t   # Gemma-2-2B prompt encode with per-stage times
