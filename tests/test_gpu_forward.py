@@ -226,3 +226,28 @@ def test_captured_step_after_many_segmentations(tmp_path):
         dit.close()
     want = nd.denoise(nd.NextDitOracle(tensors, cfg), lat[0], 16, 16, cap[0], cap_u[0], steps=3, gs=4.0)
     assert rel_l2(got[0], want) < TOL
+
+
+def test_forward_with_tracking_attention_matches_bounded(tmp_path, monkeypatch):
+    """A block's attention normally takes the bounded form (the head norm bounds every score);
+    CMFC_ATTN_FIXED_REF=0 makes it track the running row maximum instead, the form used when the
+    norm gains put the bound out of range.  Both against the oracle and against each other, with
+    jittered norm weights so the gains are not all one."""
+    from cmf_b200 import Model, NextDit
+    cfg = synth.TINY
+    path = str(tmp_path / "m.cmf")
+    tensors, _ = build(cfg, path, synth.quant_plan(cfg, oc.Q8_ROW, oc.Q8_ROW), seed=2, norm_jitter=0.2)
+    latent, cap, cap_u = _inputs(cfg, 3, 32, 32, 40, 9)
+    orc = nd.NextDitOracle(tensors, cfg)
+    wc, wu = orc.refine_caption(cap), orc.refine_caption(cap_u)
+    want_c, want_u = orc.forward_cfg_pair(latent, 32, 32, wc, wu, 0.3)
+    got = {}
+    with Model(path) as m:
+        dit = NextDit(m)
+        for env in ("1", "0"):
+            monkeypatch.setenv("CMFC_ATTN_FIXED_REF", env)
+            got[env] = dit.forward_cfg_pair(latent, 32, 32, wc, 40, wu, 9, 0.3)
+        dit.close()
+    for env in ("1", "0"):
+        assert rel_l2(got[env][0], want_c) < TOL and rel_l2(got[env][1], want_u) < TOL, env
+    assert 0 < rel_l2(got["0"][0], got["1"][0]) < 5e-3
