@@ -1231,7 +1231,7 @@ extern "C" int cmfc_bench_rowop(int kind, size_t rows, size_t cols, int iters, f
         if (kind == 0) launch_rms_mod(x.as<float>(), v0, v0 + cols, 1e-5, (int)rows, (int)cols, ob.as<__nv_bfloat16>(), nullptr, c->stream);
         else if (kind == 1) launch_gated_residual(x.as<float>(), src.as<float>(), v0, v0 + cols, 1e-5, (int)rows, (int)cols, c->stream);
         else if (kind == 2) launch_residual_then_norm(x.as<float>(), src.as<float>(), v0, v0 + cols, v0 + 2 * cols, v0 + 3 * cols, 1e-5, (int)rows, (int)cols, ob.as<__nv_bfloat16>(), c->stream);
-        else launch_qk_rope_pack(x.as<float>(), (int)rows, nh, nkv, hd, v0, v0 + hd, tab.as<float>(), tab.as<float>() + rows * hd / 2, 1.0f, ob.as<__nv_bfloat16>(), o2.as<__nv_bfloat16>(), c->stream);
+        else launch_qk_rope_pack(x.as<float>(), (int)rows, nh, nkv, hd, v0, v0 + hd, tab.as<float>(), tab.as<float>() + rows * hd / 2, 1.0f, nullptr, ob.as<__nv_bfloat16>(), o2.as<__nv_bfloat16>(), c->stream);
         c->launches++;
     };
     for (int i = 0; i < 3; ++i) run();

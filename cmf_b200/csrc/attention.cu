@@ -118,6 +118,12 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const int seg_len = p.seg_start[seg + 1] - seg0;
     const int q0 = blockIdx.x * 2 * QT;
     if (q0 >= seg_len) return;  // uniform for the CTA, before any barrier or TMEM use
+    if (p.norm2_max) {
+        // both forms were launched; the measured norms decide which one runs (2 % covers the rounding of
+        // the finished rows to bf16 and the f32 arithmetic of the measurement)
+        const float bound = sqrtf(__uint_as_float(p.norm2_max[0])) * sqrtf(__uint_as_float(p.norm2_max[1])) * 1.02f;
+        if ((bound <= ATTN_MAX_SCORE_REF) != FIXED) return;
+    }
     const int vt0 = p.seg_start[p.nseg + 1 + seg];  // first V^T column of this segment (8-aligned)
     const int kvh = head / (p.nh / p.nkv);
     const int nk = (seg_len + KT - 1) / KT;

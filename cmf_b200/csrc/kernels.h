@@ -84,6 +84,12 @@ struct AttnParams {
     // row maximum, no subtraction and no rescaling of O are needed.
     // 0: unknown bound; the kernel scales the scores itself and tracks the running row maximum.
     float score_ref = 0.0f;
+    // Decision on the device (norm2_max != nullptr): the caller could not bound the scores from the norm
+    // gains alone, measured the largest squared norms of the finished (pre-scaled) query heads and of the
+    // key heads of this launch's inputs into norm2_max[0] / [1] (float bits), and launches BOTH forms;
+    // every CTA of the form that does not apply returns at once: the bounded form runs when
+    // sqrt(norm2_max[0] * norm2_max[1]) <= ATTN_MAX_SCORE_REF, the tracking form otherwise.
+    const unsigned* norm2_max = nullptr;
 };
 constexpr float ATTN_MAX_SCORE_REF = 96.0f;
 int attn_smem_bytes(int hd);
@@ -129,8 +135,10 @@ void launch_residual_then_norm(float* x, const float* src, const float* w_res, c
 // token-major (V never passes through here: the QKV GEMM's epilogue writes V^T itself)
 // q == nullptr: only the K heads (the attention kernel then normalises and rotates Q in its prologue)
 // q_scale multiplies the finished query rows (1, or scale * log2(e) for the bounded attention form)
+// norm2_max (optional, two zeroed words): receives the largest squared norms of the finished heads
 void launch_qk_rope_pack(const float* qkv, int n, int nh, int nkv, int hd, const float* norm_q,
-                         const float* norm_k, const float* cos_t, const float* sin_t, float q_scale, __nv_bfloat16* q,
+                         const float* norm_k, const float* cos_t, const float* sin_t, float q_scale, unsigned* norm2_max,
+                         __nv_bfloat16* q,
                          __nv_bfloat16* k, cudaStream_t s);
 // y[r] = act_out( dot(W[r, :], act_in(x)) * scale[r] + b[r] ); W f32 or int8 (+row scales)
 // act_in: 0 none, 1 silu.  tanh_lo..tanh_hi: rows in [lo0,hi0) or [lo1,hi1) get tanh.

@@ -179,11 +179,15 @@ layernorm_scale_kernel(const float* __restrict__ x, const float* __restrict__ sc
 // with cos / sin tables that the host computed in f64 and rounded once (the reference rotates in
 // f64, dit.rs:1078-1102; the results here are rounded to bf16 right after).
 constexpr int ROPE_THREADS = 128;
-template <int PPL>  // hd / 32
+// MEASURE: the launch also leaves the largest squared norm of a finished query head (scale included) and
+// of a key head in norm2_max[0] / [1] (float bit patterns, atomicMax; zeroed by the caller), from which
+// attention decides on the device whether every score stays inside its bounded form's range.
+template <int PPL, bool MEASURE>  // PPL = hd / 32
 __global__ void __launch_bounds__(ROPE_THREADS, PPL <= 3 ? 8 : 4)
 qk_rope_kernel(const float* __restrict__ qkv, int n, int nh, int nkv, const float* __restrict__ norm_q,
                const float* __restrict__ norm_k, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
-               float q_scale, __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_out) {
+               float q_scale, __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_out,
+               unsigned* __restrict__ norm2_max) {
     constexpr int hd = 32 * PPL;
     const int h_first = q_out ? 0 : nh;  // without a Q output only the K heads are walked
     const int heads = nh + nkv - h_first;
@@ -210,8 +214,34 @@ qk_rope_kernel(const float* __restrict__ qkv, int n, int nh, int nkv, const floa
     ss += __shfl_xor_sync(0xffffffffu, ss, 2);
     ss += __shfl_xor_sync(0xffffffffu, ss, 1);
     const float inv = (float)(1.0 / sqrt(ss / hd + 1e-5));
-    if (!active) return;
     const float os = is_q ? q_scale : 1.0f;
+    if constexpr (MEASURE) {
+        // the rotation keeps a pair's norm, so the head's norm is that of the normalised, weighted row
+        float n2 = 0.0f;
+#pragma unroll
+        for (int g = 0; g < PPL; ++g) {
+            const float4 g0 = ld4(w + g * 32), g1 = ld4(w + g * 32 + 4);
+            const float e[8] = {rms_elem(v[g][0].x, inv, g0.x), rms_elem(v[g][0].y, inv, g0.y), rms_elem(v[g][0].z, inv, g0.z),
+                                rms_elem(v[g][0].w, inv, g0.w), rms_elem(v[g][1].x, inv, g1.x), rms_elem(v[g][1].y, inv, g1.y),
+                                rms_elem(v[g][1].z, inv, g1.z), rms_elem(v[g][1].w, inv, g1.w)};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) n2 = fmaf(e[i], e[i], n2);
+        }
+        n2 += __shfl_xor_sync(0xffffffffu, n2, 2);
+        n2 += __shfl_xor_sync(0xffffffffu, n2, 1);
+        n2 *= os * os;
+        float qm = (active && is_q) ? n2 : 0.0f, km = (active && !is_q) ? n2 : 0.0f;
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+            qm = fmaxf(qm, __shfl_xor_sync(0xffffffffu, qm, o));
+            km = fmaxf(km, __shfl_xor_sync(0xffffffffu, km, o));
+        }
+        if ((threadIdx.x & 31) == 0) {
+            if (__float_as_uint(qm) > norm2_max[0]) atomicMax(norm2_max, __float_as_uint(qm));
+            if (__float_as_uint(km) > norm2_max[1]) atomicMax(norm2_max + 1, __float_as_uint(km));
+        }
+    }
+    if (!active) return;
     __nv_bfloat16* dst = (is_q ? q_out + (size_t)tok * nh * hd + (size_t)h * hd
                                : k_out + (size_t)tok * nkv * hd + (size_t)(h - nh) * hd) + l * 8;
 #pragma unroll
@@ -513,16 +543,25 @@ bool row_cols_supported(int cols) {
     }
 }
 
+template <int PPL>
+static void rope_launch(int grid, const float* qkv, int n, int nh, int nkv, const float* norm_q, const float* norm_k,
+                        const float* cos_t, const float* sin_t, float q_scale, unsigned* norm2_max, __nv_bfloat16* q,
+                        __nv_bfloat16* k, cudaStream_t s) {
+    if (norm2_max)
+        qk_rope_kernel<PPL, true><<<grid, ROPE_THREADS, 0, s>>>(qkv, n, nh, nkv, norm_q, norm_k, cos_t, sin_t, q_scale, q, k, norm2_max);
+    else
+        qk_rope_kernel<PPL, false><<<grid, ROPE_THREADS, 0, s>>>(qkv, n, nh, nkv, norm_q, norm_k, cos_t, sin_t, q_scale, q, k, nullptr);
+}
 void launch_qk_rope_pack(const float* qkv, int n, int nh, int nkv, int hd, const float* norm_q,
-                         const float* norm_k, const float* cos_t, const float* sin_t, float q_scale, __nv_bfloat16* q,
-                         __nv_bfloat16* k, cudaStream_t s) {
+                         const float* norm_k, const float* cos_t, const float* sin_t, float q_scale, unsigned* norm2_max,
+                         __nv_bfloat16* q, __nv_bfloat16* k, cudaStream_t s) {
     const long items = (long)n * ((q ? nh : 0) + nkv);
     const int grid = (int)((items + ROPE_THREADS / 4 - 1) / (ROPE_THREADS / 4));
     switch (hd / 32) {
-        case 1: qk_rope_kernel<1><<<grid, ROPE_THREADS, 0, s>>>(qkv, n, nh, nkv, norm_q, norm_k, cos_t, sin_t, q_scale, q, k); break;
-        case 2: qk_rope_kernel<2><<<grid, ROPE_THREADS, 0, s>>>(qkv, n, nh, nkv, norm_q, norm_k, cos_t, sin_t, q_scale, q, k); break;
-        case 3: qk_rope_kernel<3><<<grid, ROPE_THREADS, 0, s>>>(qkv, n, nh, nkv, norm_q, norm_k, cos_t, sin_t, q_scale, q, k); break;
-        case 4: qk_rope_kernel<4><<<grid, ROPE_THREADS, 0, s>>>(qkv, n, nh, nkv, norm_q, norm_k, cos_t, sin_t, q_scale, q, k); break;
+        case 1: rope_launch<1>(grid, qkv, n, nh, nkv, norm_q, norm_k, cos_t, sin_t, q_scale, norm2_max, q, k, s); break;
+        case 2: rope_launch<2>(grid, qkv, n, nh, nkv, norm_q, norm_k, cos_t, sin_t, q_scale, norm2_max, q, k, s); break;
+        case 3: rope_launch<3>(grid, qkv, n, nh, nkv, norm_q, norm_k, cos_t, sin_t, q_scale, norm2_max, q, k, s); break;
+        case 4: rope_launch<4>(grid, qkv, n, nh, nkv, norm_q, norm_k, cos_t, sin_t, q_scale, norm2_max, q, k, s); break;
         default: break;
     }
 }

@@ -724,7 +724,7 @@ int attention_score_ref(Context* c, const __nv_bfloat16* q, const __nv_bfloat16*
 
 int dev_attention(Context* c, const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* vt,
                   const SegTable& st, int nh, int nkv, int hd, float scale, __nv_bfloat16* out, const AttnRawQ* raw,
-                  float score_ref) {
+                  float score_ref, const unsigned* norm2_max) {
     if (hd % 32 || hd > 128 || hd < 32) return fail(ERR_UNSUPPORTED, "attention needs head_dim in {32, 64, 96, 128}");
     if (nh % nkv) return fail(ERR_BAD_ARG, "query heads must be a multiple of kv heads");
     CUtensorMap tm_q, tm_k, tm_vt;
@@ -736,7 +736,7 @@ int dev_attention(Context* c, const __nv_bfloat16* q, const __nv_bfloat16* k, co
     AttnParams p;
     p.nh = nh; p.nkv = nkv; p.hd = hd; p.n_total = st.n_total; p.vt_pitch = st.vt_pitch;
     p.seg_start = st.dev; p.nseg = (int)st.host.size(); p.max_seg = st.max_seg; p.scale = scale;
-    p.out = out; p.status = c->status; p.score_ref = score_ref;
+    p.out = out; p.status = c->status; p.score_ref = score_ref; p.norm2_max = norm2_max;
     if (raw) {
         if ((reinterpret_cast<uintptr_t>(raw->q_raw) & 15) || raw->ld_q % 4)
             return fail(ERR_BAD_ARG, "attention: the raw query rows must be 16-byte aligned");
@@ -790,20 +790,39 @@ int dev_block(Context* c, const BlockWeights& bw, const BlockMod& mod, float* x,
     const bool q_prologue = pro_env && pro_env[0] == '1';
     // the head norm bounds every score, so attention can take the bounded form (AttnParams::score_ref),
     // whose queries come multiplied by scale * log2(e)
-    const float attn_scale = 1.0f / sqrtf((float)hd);
+    const float attn_scale = 1.0f / sqrtf((float)hd), log2e = 1.4426950408889634f;
     const float score_ref = attention_score_ref_from_gain(bw.qk_gain, hd);
+    // Norm gains too large for that bound say little about real rows (the worst case puts a whole row's
+    // weight on the largest gain): then the pass measures the finished heads and attention decides on the
+    // device, both forms launched, one of them returning at once.
+    const bool measured = score_ref == 0.0f && bw.qk_gain > 0.0f && fixed_ref_enabled() && !q_prologue;
+    unsigned* norm2 = nullptr;
+    if (measured) {
+        DevBuf& nb = c->lane_buf("attn_norm2");
+        CMFC_TRY(nb.ensure(8));
+        CMFC_CUDA(cudaMemsetAsync(nb.p, 0, 8, s));
+        norm2 = nb.as<unsigned>();
+    }
     {
         SpanGuard g(c, "rope");
         launch_qk_rope_pack(qkv.as<float>(), n, nh, nkv, hd, bw.norm_q, bw.norm_k, cos_t, sin_t,
-                            score_ref > 0.0f ? attn_scale * 1.4426950408889634f : 1.0f,
+                            (score_ref > 0.0f || measured) ? attn_scale * log2e : 1.0f, norm2,
                             q_prologue ? nullptr : qb.as<__nv_bfloat16>(), kb.as<__nv_bfloat16>(), s);
         c->launches++;
     }
     {
         SpanGuard g(c, "attention");
         const AttnRawQ raw = {qkv.as<float>(), qkv_w, bw.norm_q, cos_t, sin_t};
-        CMFC_TRY(dev_attention(c, qb.as<__nv_bfloat16>(), kb.as<__nv_bfloat16>(), vt.as<__nv_bfloat16>(), st, nh, nkv, hd,
-                               attn_scale, att.as<__nv_bfloat16>(), q_prologue ? &raw : nullptr, score_ref));
+        if (measured) {
+            // the queries are pre-scaled either way: the tracking form gets scale * log2(e) = 1
+            CMFC_TRY(dev_attention(c, qb.as<__nv_bfloat16>(), kb.as<__nv_bfloat16>(), vt.as<__nv_bfloat16>(), st, nh, nkv, hd,
+                                   attn_scale, att.as<__nv_bfloat16>(), nullptr, ATTN_MAX_SCORE_REF, norm2));
+            CMFC_TRY(dev_attention(c, qb.as<__nv_bfloat16>(), kb.as<__nv_bfloat16>(), vt.as<__nv_bfloat16>(), st, nh, nkv, hd,
+                                   1.0f / log2e, att.as<__nv_bfloat16>(), nullptr, 0.0f, norm2));
+        } else {
+            CMFC_TRY(dev_attention(c, qb.as<__nv_bfloat16>(), kb.as<__nv_bfloat16>(), vt.as<__nv_bfloat16>(), st, nh, nkv, hd,
+                                   attn_scale, att.as<__nv_bfloat16>(), q_prologue ? &raw : nullptr, score_ref));
+        }
     }
     {
         SpanGuard g(c, "o-proj");

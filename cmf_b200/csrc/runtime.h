@@ -153,7 +153,7 @@ struct AttnRawQ {
 // score_ref: AttnParams::score_ref (0: the kernel tracks the row maximum)
 int dev_attention(Context* c, const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* vt,
                   const SegTable& st, int nh, int nkv, int hd, float scale, __nv_bfloat16* out,
-                  const AttnRawQ* raw = nullptr, float score_ref = 0.0f);
+                  const AttnRawQ* raw = nullptr, float score_ref = 0.0f, const unsigned* norm2_max = nullptr);
 // Measures max |q_i| and max |k_j| over finished bf16 rows on the device (one small launch each and a
 // synchronizing 8-byte read: not for a captured stream) and returns the fixed softmax reference they
 // allow, or 0 when it would exceed ATTN_MAX_SCORE_REF or CMFC_ATTN_FIXED_REF=0 is set.

@@ -8,10 +8,12 @@ from oracle.nextdit import QWeight
 from tests import synth
 
 
-def build(cfg, path, plan, seed=0, norm_jitter=0.0, std=0.02):
+def build(cfg, path, plan, seed=0, norm_jitter=0.0, std=0.02, mutate=None):
     """Returns (tensors_for_oracle, config_json).  ``plan`` maps tensor name -> dtype id; every
-    other tensor stays f32."""
+    other tensor stays f32.  ``mutate(tensors)`` may edit the f32 tensors before they are quantized."""
     t = synth.make_tensors(cfg, seed, norm_jitter, std)
+    if mutate is not None:
+        mutate(t)
     w = CmfWriter(arch={"arch_name": "nextdit-synth", "hidden_size": cfg["hidden_size"],
                         "num_layers": cfg["num_layers"], "vocab_size": 0})
     oracle_t = {}

@@ -251,3 +251,41 @@ def test_forward_with_tracking_attention_matches_bounded(tmp_path, monkeypatch):
     for env in ("1", "0"):
         assert rel_l2(got[env][0], want_c) < TOL and rel_l2(got[env][1], want_u) < TOL, env
     assert 0 < rel_l2(got["0"][0], got["1"][0]) < 5e-3
+
+
+@pytest.mark.parametrize("case", ["one_large_gain", "all_gains_large"])
+def test_forward_with_norm_gains_beyond_the_weight_bound(tmp_path, monkeypatch, case):
+    """Head-norm gains so large that the worst case they allow (a whole row's weight on the largest gain)
+    exceeds the bounded attention form's range.  The qk-norm + RoPE pass then measures the finished
+    heads and attention decides on the device: with ONE gain of 5 in the query norm and one in the key norm
+    (worst-case bound 294 log2 units) real rows measure about 50 and the bounded form runs; with ALL gains
+    3.5 they measure 144 and the tracking form runs.  Either way the result
+    must equal the forced tracking form; against the oracle the tolerance is wider than elsewhere
+    because logits this large amplify the bf16 rounding of Q and K."""
+    from cmf_b200 import Model, NextDit
+    cfg = synth.TINY
+
+    def mutate(t):
+        for name in t:
+            if name.endswith("attn.norm_q.weight") or name.endswith("attn.norm_k.weight"):
+                if case == "one_large_gain":
+                    t[name][3 if name.endswith("norm_q.weight") else 5] = 5.0
+                else:
+                    t[name] *= 3.5
+
+    path = str(tmp_path / "m.cmf")
+    tensors, _ = build(cfg, path, synth.quant_plan(cfg, oc.Q8_ROW, oc.Q8_ROW), seed=5, mutate=mutate)
+    latent, cap, cap_u = _inputs(cfg, 4, 32, 32, 40, 9)
+    orc = nd.NextDitOracle(tensors, cfg)
+    wc, wu = orc.refine_caption(cap), orc.refine_caption(cap_u)
+    want_c, _ = orc.forward_cfg_pair(latent, 32, 32, wc, wu, 0.4)
+    got = {}
+    with Model(path) as m:
+        dit = NextDit(m)
+        for env in ("1", "0"):
+            monkeypatch.setenv("CMFC_ATTN_FIXED_REF", env)
+            got[env] = dit.forward_cfg_pair(latent, 32, 32, wc, 40, wu, 9, 0.4)[0]
+        dit.close()
+    assert np.isfinite(got["1"]).all()
+    assert rel_l2(got["1"], got["0"]) < 5e-3, rel_l2(got["1"], got["0"])
+    assert rel_l2(got["1"], want_c) < 5e-2, rel_l2(got["1"], want_c)
