@@ -289,3 +289,17 @@ def test_forward_with_norm_gains_beyond_the_weight_bound(tmp_path, monkeypatch, 
     assert np.isfinite(got["1"]).all()
     assert rel_l2(got["1"], got["0"]) < 5e-3, rel_l2(got["1"], got["0"])
     assert rel_l2(got["1"], want_c) < 5e-2, rel_l2(got["1"], want_c)
+    # the same through the captured step (the measurement's memset and both launches are graph nodes)
+    from cmf_b200 import GenParams, denoise
+    lat = nd.gauss_latent(16 * 16 * 16, 1).reshape(1, 16, 16, 16)
+    loops = {}
+    with Model(path) as m:
+        dit = NextDit(m)
+        for env in ("1", "0"):
+            monkeypatch.setenv("CMFC_ATTN_FIXED_REF", env)
+            loops[env] = denoise(dit, lat, cap[None], cap_u[None], GenParams(steps=4, guidance_scale=4.0))
+        dit.close()
+    # four guided steps (guidance scale 4) on logits this large amplify the different bf16 rounding of
+    # the queries (pre-scaled here, unscaled in the forced form): a wider tolerance than for one forward
+    assert np.isfinite(loops["1"]).all()
+    assert rel_l2(loops["1"], loops["0"]) < 3e-2, rel_l2(loops["1"], loops["0"])
