@@ -448,7 +448,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     for (int i = 0; i < CW; i += 2) {
                         const float t0 = __uint_as_float(v[ch][i]), t1 = __uint_as_float(v[ch][i + 1]);
                         float e0, e1;
-                        if (((i >> 1) & 7) < POLY_OF_8) {
+                        // the polynomial pairs spread among the others (pairs 0, 3, 6 of eight for POLY_OF_8 = 3)
+                        if ((((i >> 1) & 7) * POLY_OF_8) % 8 < POLY_OF_8) {
                             ex2_poly_x2<false>(t0, t1, e0, e1);
                         } else {
                             e0 = ex2_approx(t0);
